@@ -34,6 +34,7 @@ RELEASED = -1
 class GroupPolicy:
     page_tokens: int
     window: Optional[int] = None     # None: keep every token
+    keep_first: int = 0              # with a window: the first tokens stay visible, their pages stay
 
 
 def _opt(value: Optional[int]) -> int:
@@ -63,7 +64,8 @@ class CacheManager:
             n, arr(p.page_tokens for p in self.policies), arr(_opt(p.window) for p in self.policies),
             arr(pages_per_group), n_state_slots,
             arr(table_strides) if table_strides is not None else None,
-            arr(null_pages) if null_pages is not None else None)
+            arr(null_pages) if null_pages is not None else None,
+            arr(p.keep_first for p in self.policies))
         if not self._h:
             raise ValueError("the cache manager's sizes must be positive")
         self.table_strides = tuple(table_strides) if table_strides is not None else None

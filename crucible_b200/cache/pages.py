@@ -29,7 +29,7 @@ def native():
             ("cb_stack_create", vp, [i]), ("cb_stack_destroy", None, [vp]),
             ("cb_stack_take", i, [vp]), ("cb_stack_give", i, [vp, i]),
             ("cb_stack_free", i, [vp]), ("cb_stack_in_use", i, [vp, i]),
-            ("cb_cache_create", vp, [i, vp, vp, vp, i, vp, vp]), ("cb_cache_destroy", None, [vp]),
+            ("cb_cache_create", vp, [i, vp, vp, vp, i, vp, vp, vp]), ("cb_cache_destroy", None, [vp]),
             ("cb_cache_stack", vp, [vp, i]), ("cb_cache_pages_for", l, [vp, i, l, l]),
             ("cb_cache_fits", i, [vp, l, l, i]), ("cb_cache_add", i, [vp, l, l, vp, cp, i]),
             ("cb_cache_extend", i, [vp, i, l, cp, i]), ("cb_cache_shrink", i, [vp, i, l]),

@@ -20,6 +20,11 @@ from dataclasses import dataclass, field
 from typing import Any, Mapping, Optional, Tuple
 
 
+# `max_context` of a design that names no longest context: the engine then bounds a request
+# by its options or by its page pool.
+UNBOUNDED_CONTEXT = 1 << 30
+
+
 class ConfigError(ValueError):
     """A config.json that cannot be executed; the message names the key."""
 
@@ -76,6 +81,10 @@ class LayerSpec:
     mixer: MixerSpec
     feed_forward: FeedForwardSpec
     norms: Tuple[Tuple[str, NormSpec], ...]
+    extra: Tuple[Tuple[str, Any], ...] = ()     # free-form options of the arrangement
+
+    def option(self, key: str, default: Any = None) -> Any:
+        return dict(self.extra).get(key, default)
 
     def norm(self, name: str) -> NormSpec:
         for key, spec in self.norms:

@@ -77,6 +77,8 @@ struct Stack {
 struct Group {
     int page_tokens;
     int window;          // < 0: every token is kept
+    int keep_first;      // with a window: the request's first tokens stay visible, so the
+                         // pages that hold them are never given back early
     int stride;          // ints of a device table row; 0: no rows are kept
     int null_page;       // what a row holds in place of a page given back early
     long reserved;
@@ -84,8 +86,8 @@ struct Group {
     std::vector<int32_t> rows;    // n_slots * stride
     std::vector<int32_t> owner;   // per page: the slot whose table names it, or -1
 
-    Group(int pt, int w, int n_pages, int st, int np, int n_slots)
-        : page_tokens(pt), window(w), stride(st), null_page(np), reserved(0), pool(n_pages),
+    Group(int pt, int w, int kf, int n_pages, int st, int np, int n_slots)
+        : page_tokens(pt), window(w), keep_first(kf), stride(st), null_page(np), reserved(0), pool(n_pages),
           rows((size_t)n_slots * st, 0), owner(n_pages, -1) {}
 };
 
@@ -121,7 +123,8 @@ long pages_for(const Group& g, long n_tokens, long max_step) {
     }
     // the window's keys before the step's first token, the step itself, and one page
     // for misalignment at either end
-    const long live = ceil_div(g.window - 1 + step, g.page_tokens) + 1;
+    const long live = ceil_div(g.window - 1 + step, g.page_tokens) + 1 +
+                      ceil_div(g.keep_first, g.page_tokens);
     return full < live ? full : live;
 }
 
@@ -147,7 +150,10 @@ int release_passed(Cache& c, int slot) {
         long upto = first_needed / g.page_tokens;
         std::vector<int>& table = r.tables[gi];
         if (upto > (long)table.size()) upto = (long)table.size();
-        for (long b = r.first_live[gi]; b < upto; ++b) {
+        // the pages of the kept first tokens stay
+        long from = ceil_div(g.keep_first, g.page_tokens);
+        if (from < r.first_live[gi]) from = r.first_live[gi];
+        for (long b = from; b < upto; ++b) {
             if (table[b] != RELEASED) {
                 const int code = give_back(g, slot, table[b]);
                 if (code != OK && result == OK) result = code;
@@ -312,16 +318,19 @@ CB_EXPORT int cb_stack_in_use(void* s, int id) {
 
 // windows[g] < 0: the group keeps every token.  strides: ints of a device table row per
 // group (null or 0: no rows kept); null_pages: what a row holds for a page given back early.
+// keep_first (may be null: none): tokens at the start of a request that a windowed group keeps.
 CB_EXPORT void* cb_cache_create(int n_groups, const int32_t* page_tokens, const int32_t* windows,
                                 const int32_t* n_pages, int n_slots, const int32_t* strides,
-                                const int32_t* null_pages) {
+                                const int32_t* null_pages, const int32_t* keep_first) {
     if (n_groups < 0 || n_slots <= 0) return nullptr;
     for (int g = 0; g < n_groups; ++g)
         if (page_tokens[g] <= 0 || n_pages[g] <= 0 || (strides && strides[g] < 0)) return nullptr;
     Cache* c = new Cache(n_slots);
     c->groups.reserve(n_groups);
     for (int g = 0; g < n_groups; ++g)
-        c->groups.emplace_back(page_tokens[g], windows[g], n_pages[g], strides ? strides[g] : 0,
+        c->groups.emplace_back(page_tokens[g], windows[g],
+                               keep_first && keep_first[g] > 0 ? keep_first[g] : 0, n_pages[g],
+                               strides ? strides[g] : 0,
                                null_pages ? null_pages[g] : 0, n_slots);
     return c;
 }

@@ -1,0 +1,422 @@
+// Mixers that carry a matrix of fixed size per head from token to token instead of
+// a cache of keys: the gated delta rule and the matrix memory with exponential gates
+// (mLSTM).  Per request and head the state is S [D][E] in fp32 (mLSTM also n [D] and
+// a running maximum m); it lives in the request's state slot and is read at the
+// start of a step and written at its end, so a prompt may be cut anywhere.
+//
+//   delta rule, per token:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//   mLSTM, per token:       m' = max(f + m, i);  a = exp(f + m - m');  b = exp(i - m');
+//                           S <- a S + b k v^T;  n <- a n + b k;
+//                           o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+//
+// Kernels: the preparation of a step's rows (for the delta rule: a short causal
+// convolution over time per channel, whose last taps - 1 inputs are state too,
+// SiLU, unit vectors per head, and the gates; for the mLSTM: the capped gates), the
+// update of the convolution's state, the recurrence itself, and the per-head RMS
+// norm with gain and output gate.  Everything after the projections is fp32.
+//
+// The recurrence walks a request's tokens in order.  A block owns 32 columns of one
+// head's S; four lanes share a column, each with a quarter of its D entries in
+// registers, so a token costs two passes of D/4 multiply-adds and two shuffles.
+// The tokens' q, k, v and gates are staged in shared memory 16 tokens at a time.
+#define CB_PDL_BIT 11      // this file's bit in CRUCIBLE_PDL
+#include "common.cuh"
+
+namespace {
+
+constexpr int RULE_DELTA = 0, RULE_MLSTM = 1;
+constexpr int GATE_SILU = 0, GATE_SIGMOID = 1;
+constexpr int COLS = 32;          // columns of S per block
+constexpr int CHUNK = 16;         // tokens staged at a time
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float logsigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+__device__ __forceinline__ float* state_at(unsigned char* state, long slot_stride, int slot, long off) {
+    return reinterpret_cast<float*>(state + (size_t)slot * slot_stride + off);
+}
+
+// ---- delta rule: convolution + SiLU, unit q and k, gates ---------------------------------
+// proj row: [q: G*D | k: G*D | v: H*E | ...] in T.  conv_w: fp32 [C][taps], the last column
+// meets the current token.  The request's state holds the last taps - 1 inputs of every
+// channel, oldest first, fp32 [taps-1][C].  gates: fp32 [rows][2H] = [beta logits | rate logits].
+template <typename T>
+__global__ void delta_prepare_kernel(const T* __restrict__ proj, int proj_stride,
+                                     const float* __restrict__ conv_w, int taps,
+                                     const float* __restrict__ gates, int gates_stride,
+                                     const float* __restrict__ a_log,
+                                     const float* __restrict__ dt_bias,
+                                     const int* __restrict__ row_request,
+                                     const int* __restrict__ req_row_start,
+                                     const int* __restrict__ req_state_slot, unsigned char* state,
+                                     long slot_stride, long tail_off, float* __restrict__ qkv,
+                                     float* __restrict__ beta, float* __restrict__ decay, int n_heads,
+                                     int n_kv_heads, int key_dim, int value_dim) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    extern __shared__ float row[];
+    const int t = blockIdx.x;
+    const int r = row_request[t];
+    const int first = req_row_start[r];
+    const int local = t - first;
+    const int C = 2 * n_kv_heads * key_dim + n_heads * value_dim;
+    const float* tail = state_at(state, slot_stride, req_state_slot[r], tail_off);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = local - (taps - 1) + j;
+            const float x = src >= 0 ? cb_to_float(proj[(size_t)(first + src) * proj_stride + c])
+                                     : tail[(size_t)(taps - 1 + src) * C + c];
+            acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+        }
+        row[c] = silu_f(acc);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    // q heads then k heads: unit vectors; q also times D^-1/2
+    const float q_scale = 1.0f / sqrtf((float)key_dim);
+    for (int h = warp; h < 2 * n_kv_heads; h += n_warps) {
+        float* v = row + (size_t)h * key_dim;
+        float ss = 0.f;
+        for (int d = lane; d < key_dim; d += 32) ss = fmaf(v[d], v[d], ss);
+        float inv = 1.0f / sqrtf(cb_warp_sum(ss) + 1e-6f);
+        if (h < n_kv_heads) inv *= q_scale;
+        for (int d = lane; d < key_dim; d += 32) v[d] *= inv;
+    }
+    __syncthreads();
+    float* dst = qkv + (size_t)t * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] = row[c];
+    for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
+        const float* g = gates + (size_t)t * gates_stride;
+        beta[(size_t)t * n_heads + h] = sigmoid_f(g[h]);
+        decay[(size_t)t * n_heads + h] = expf(-expf(a_log[h]) * softplus_f(g[n_heads + h] + dt_bias[h]));
+    }
+}
+
+// After a step: the convolution's state becomes the last taps - 1 inputs seen.
+template <typename T>
+__global__ void conv_tail_update_kernel(const T* __restrict__ proj, int proj_stride, int taps, int C,
+                                        const int* __restrict__ req_row_start,
+                                        const int* __restrict__ req_state_slot, unsigned char* state,
+                                        long slot_stride, long tail_off) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int r = blockIdx.x;
+    const int first = req_row_start[r], n_new = req_row_start[r + 1] - first;
+    float* tail = state_at(state, slot_stride, req_state_slot[r], tail_off);
+    const int keep = taps - 1;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        for (int i = 0; i < keep; ++i) {          // ascending: reads run ahead of writes
+            const int src = n_new - keep + i;
+            tail[(size_t)i * C + c] = src >= 0 ? cb_to_float(proj[(size_t)(first + src) * proj_stride + c])
+                                               : tail[(size_t)(i + n_new) * C + c];
+        }
+    }
+}
+
+// ---- mLSTM: q * D^-1/2, k, v to fp32 and the capped log gates -----------------------------
+// proj row: [q: H*D | k: H*D | v: H*E | ...]; gates: fp32 [rows][2H] = [input | forget] logits.
+template <typename T>
+__global__ void mlstm_prepare_kernel(const T* __restrict__ proj, int proj_stride,
+                                     const float* __restrict__ gates, int gates_stride,
+                                     const float* __restrict__ bias_i,
+                                     const float* __restrict__ bias_f, float cap, float* __restrict__ qkv,
+                                     float* __restrict__ log_keep, float* __restrict__ log_in,
+                                     int n_heads, int key_dim, int value_dim) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int t = blockIdx.x;
+    const int nq = n_heads * key_dim, C = 2 * nq + n_heads * value_dim;
+    const float q_scale = 1.0f / sqrtf((float)key_dim);
+    const T* src = proj + (size_t)t * proj_stride;
+    float* dst = qkv + (size_t)t * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float x = cb_to_float(src[c]);
+        dst[c] = c < nq ? x * q_scale : x;
+    }
+    for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
+        const float* g = gates + (size_t)t * gates_stride;
+        log_in[(size_t)t * n_heads + h] = cap * tanhf((g[h] + bias_i[h]) / cap);
+        log_keep[(size_t)t * n_heads + h] = logsigmoid_f(cap * tanhf((g[n_heads + h] + bias_f[h]) / cap));
+    }
+}
+
+// ---- the recurrence ----------------------------------------------------------------------
+// qkv: fp32 [rows][C] with q heads at q_off, k heads at k_off (both n_qk_heads of D), v heads at
+// v_off (n_heads of E).  sc0, sc1: fp32 [rows][H]: (decay, beta) or (log keep, log in).
+// State: S at s_off [H][D][E]; mLSTM: n at n_off [H][D], m at m_off [H].
+template <int P, int RULE>
+__global__ void __launch_bounds__(128) matrix_memory_kernel(
+    const float* __restrict__ qkv, int C, int q_off, int k_off, int v_off,
+    const float* __restrict__ sc0, const float* __restrict__ sc1,
+    const int* __restrict__ req_row_start, const int* __restrict__ req_state_slot,
+    unsigned char* state, long slot_stride, long s_off, long n_off, long m_off,
+    float* __restrict__ out, int n_heads, int n_qk_heads, int D, int E) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    extern __shared__ float stage[];
+    float* sk = stage;                       // [CHUNK][D]
+    float* sq = sk + CHUNK * D;              // [CHUNK][D]
+    float* sv = sq + CHUNK * D;              // [CHUNK][COLS]
+    float* s0 = sv + CHUNK * COLS;           // [CHUNK]
+    float* s1 = s0 + CHUNK;                  // [CHUNK]
+    const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * COLS;
+    const int g = head / (n_heads / n_qk_heads);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col = col0 + warp * 8 + (lane >> 2), part = lane & 3;
+    const bool live = col < E;
+    const int row0 = req_row_start[r], row1 = req_row_start[r + 1];
+    const int slot = req_state_slot[r];
+    float* S = state_at(state, slot_stride, slot, s_off) + (size_t)head * D * E;
+    float* N = RULE == RULE_MLSTM ? state_at(state, slot_stride, slot, n_off) + (size_t)head * D : nullptr;
+    float* M = RULE == RULE_MLSTM ? state_at(state, slot_stride, slot, m_off) + head : nullptr;
+    float s[P], n[P];
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+        const int d = part + 4 * i;
+        s[i] = (live && d < D) ? S[(size_t)d * E + col] : 0.f;
+        n[i] = (RULE == RULE_MLSTM && d < D) ? N[d] : 0.f;
+    }
+    if (RULE == RULE_MLSTM) m = *M;
+    for (int base = row0; base < row1; base += CHUNK) {
+        const int cnt = min(CHUNK, row1 - base);
+        __syncthreads();
+        for (int i = threadIdx.x; i < cnt * D; i += blockDim.x) {
+            const int tt = i / D, d = i - tt * D;
+            const float* src = qkv + (size_t)(base + tt) * C + (size_t)g * D + d;
+            sk[tt * D + d] = src[k_off];
+            sq[tt * D + d] = src[q_off];
+        }
+        for (int i = threadIdx.x; i < cnt * COLS; i += blockDim.x) {
+            const int tt = i / COLS, c = i - tt * COLS;
+            sv[i] = col0 + c < E ? qkv[(size_t)(base + tt) * C + v_off + (size_t)head * E + col0 + c] : 0.f;
+        }
+        if (threadIdx.x < cnt) {
+            s0[threadIdx.x] = sc0[(size_t)(base + threadIdx.x) * n_heads + head];
+            s1[threadIdx.x] = sc1[(size_t)(base + threadIdx.x) * n_heads + head];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < cnt; ++tt) {
+            const float* kk = sk + tt * D;
+            const float* qq = sq + tt * D;
+            const float v = sv[tt * COLS + (col - col0)];
+            float o;
+            if (RULE == RULE_DELTA) {
+                const float decay = s0[tt], beta = s1[tt];
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < P; ++i) {
+                    const int d = part + 4 * i;
+                    s[i] *= decay;
+                    if (d < D) acc[i & 3] = fmaf(s[i], kk[d], acc[i & 3]);
+                }
+                float rk = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                rk += __shfl_xor_sync(0xffffffffu, rk, 1);
+                rk += __shfl_xor_sync(0xffffffffu, rk, 2);
+                const float u = beta * (v - rk);
+                float oc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < P; ++i) {
+                    const int d = part + 4 * i;
+                    if (d < D) {
+                        s[i] = fmaf(kk[d], u, s[i]);
+                        oc[i & 3] = fmaf(s[i], qq[d], oc[i & 3]);
+                    }
+                }
+                o = (oc[0] + oc[1]) + (oc[2] + oc[3]);
+                o += __shfl_xor_sync(0xffffffffu, o, 1);
+                o += __shfl_xor_sync(0xffffffffu, o, 2);
+            } else {
+                const float f = s0[tt], in = s1[tt];
+                const float m_new = fmaxf(f + m, in);
+                const float a = expf(f + m - m_new), b = expf(in - m_new);
+                m = m_new;
+                const float bv = b * v;
+                float oc[4] = {0.f, 0.f, 0.f, 0.f}, nc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < P; ++i) {
+                    const int d = part + 4 * i;
+                    if (d < D) {
+                        const float kd = kk[d], qd = qq[d];
+                        s[i] = fmaf(kd, bv, a * s[i]);
+                        n[i] = fmaf(b, kd, a * n[i]);
+                        oc[i & 3] = fmaf(s[i], qd, oc[i & 3]);
+                        nc[i & 3] = fmaf(n[i], qd, nc[i & 3]);
+                    }
+                }
+                o = (oc[0] + oc[1]) + (oc[2] + oc[3]);
+                float nq = (nc[0] + nc[1]) + (nc[2] + nc[3]);
+                o += __shfl_xor_sync(0xffffffffu, o, 1);
+                nq += __shfl_xor_sync(0xffffffffu, nq, 1);
+                o += __shfl_xor_sync(0xffffffffu, o, 2);
+                nq += __shfl_xor_sync(0xffffffffu, nq, 2);
+                o = o / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
+            }
+            if (live && part == 0) out[(size_t)(base + tt) * n_heads * E + (size_t)head * E + col] = o;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+        const int d = part + 4 * i;
+        if (live && d < D) S[(size_t)d * E + col] = s[i];
+        if (RULE == RULE_MLSTM && blockIdx.z == 0 && col == 0 && d < D) N[d] = n[i];
+    }
+    if (RULE == RULE_MLSTM && blockIdx.z == 0 && threadIdx.x == 0) *M = m;
+}
+
+// ---- per-head RMS norm, gain and output gate ----------------------------------------------
+// o: fp32 [rows][H*E].  gain: [E] shared by the heads (gain_head_stride 0) or [H*E].
+// gate: T rows (the joint projection) at a column offset.  out: T rows at a column offset.
+template <typename T, int GATE>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gain,
+                                      int gain_head_stride, const T* __restrict__ gate, int gate_stride,
+                                      T* __restrict__ out, int out_stride, int n_rows, int n_heads,
+                                      int E, float eps, float out_scale) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= n_rows * n_heads) return;
+    const int lane = threadIdx.x & 31;
+    const int t = unit / n_heads, h = unit - t * n_heads;
+    const float* src = o + (size_t)t * n_heads * E + (size_t)h * E;
+    float ss = 0.f;
+    for (int e = lane; e < E; e += 32) ss = fmaf(src[e], src[e], ss);
+    const float r = 1.0f / sqrtf(cb_warp_sum(ss) / (float)E + eps);
+    const T* grow = gate + (size_t)t * gate_stride + (size_t)h * E;
+    T* dst = out + (size_t)t * out_stride + (size_t)h * E;
+    const float* gn = gain + (size_t)h * gain_head_stride;
+    for (int e = lane; e < E; e += 32) {
+        const float z = cb_to_float(grow[e]);
+        const float gt = GATE == GATE_SILU ? silu_f(z) : sigmoid_f(z);
+        dst[e] = cb_from_float<T>(src[e] * r * gn[e] * gt * out_scale);
+    }
+}
+
+template <int RULE>
+int launch_memory(const float* qkv, int C, int q_off, int k_off, int v_off, const float* sc0,
+                  const float* sc1, const int* req_row_start, const int* req_state_slot,
+                  unsigned char* state, long slot_stride, long s_off, long n_off, long m_off, float* out,
+                  int n_requests, int n_heads, int n_qk_heads, int D, int E, cudaStream_t s) {
+    const dim3 grid(n_requests, n_heads, (E + COLS - 1) / COLS), block(128);
+    const size_t smem = (size_t)(CHUNK * (2 * D + COLS) + 2 * CHUNK) * sizeof(float);
+#define CB_MEM(PP)                                                                                 \
+    cb_launch(matrix_memory_kernel<PP, RULE>, grid, block, smem, s, qkv, C, q_off, k_off, v_off, sc0, \
+              sc1, req_row_start, req_state_slot, state, slot_stride, s_off, n_off, m_off, out,     \
+              n_heads, n_qk_heads, D, E)
+    if (D <= 32) CB_MEM(8);
+    else if (D <= 64) CB_MEM(16);
+    else if (D <= 128) CB_MEM(32);
+    else if (D <= 256) CB_MEM(64);
+    else return CB_ERR_UNSUPPORTED;
+#undef CB_MEM
+    return cb_last_error();
+}
+
+}  // namespace
+
+CB_EXPORT int cb_delta_prepare(const void* proj, int proj_stride, int dtype, const float* conv_w,
+                               int taps, const float* gates, int gates_stride, const float* a_log,
+                               const float* dt_bias,
+                               const int* row_request, const int* req_row_start,
+                               const int* req_state_slot, void* state, long slot_stride, long tail_off,
+                               float* qkv, float* beta, float* decay, int n_rows, int n_heads,
+                               int n_kv_heads, int key_dim, int value_dim, void* stream) {
+    if (n_rows <= 0) return 0;
+    const int C = 2 * n_kv_heads * key_dim + n_heads * value_dim;
+    if (taps < 1 || C > 12000 || n_heads % n_kv_heads != 0) return CB_ERR_UNSUPPORTED;
+    const dim3 grid(n_rows), block(C <= 1024 ? 128 : 256);
+    const size_t smem = (size_t)C * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(delta_prepare_kernel<float>, grid, block, smem, s, (const float*)proj, proj_stride,
+                  conv_w, taps, gates, gates_stride, a_log, dt_bias, row_request, req_row_start, req_state_slot,
+                  (unsigned char*)state, slot_stride, tail_off, qkv, beta, decay, n_heads, n_kv_heads,
+                  key_dim, value_dim);
+    else
+        cb_launch(delta_prepare_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)proj,
+                  proj_stride, conv_w, taps, gates, gates_stride, a_log, dt_bias, row_request, req_row_start,
+                  req_state_slot, (unsigned char*)state, slot_stride, tail_off, qkv, beta, decay,
+                  n_heads, n_kv_heads, key_dim, value_dim);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_conv_tail_update(const void* proj, int proj_stride, int dtype, int taps, int C,
+                                  const int* req_row_start, const int* req_state_slot, void* state,
+                                  long slot_stride, long tail_off, int n_requests, void* stream) {
+    if (n_requests <= 0 || taps <= 1) return 0;
+    const dim3 grid(n_requests, (C + 127) / 128), block(128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(conv_tail_update_kernel<float>, grid, block, 0, s, (const float*)proj, proj_stride,
+                  taps, C, req_row_start, req_state_slot, (unsigned char*)state, slot_stride, tail_off);
+    else
+        cb_launch(conv_tail_update_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)proj,
+                  proj_stride, taps, C, req_row_start, req_state_slot, (unsigned char*)state,
+                  slot_stride, tail_off);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_mlstm_prepare(const void* proj, int proj_stride, int dtype, const float* gates,
+                               int gates_stride, const float* bias_i, const float* bias_f, float cap, float* qkv,
+                               float* log_keep, float* log_in, int n_rows, int n_heads, int key_dim,
+                               int value_dim, void* stream) {
+    if (n_rows <= 0) return 0;
+    const dim3 grid(n_rows), block(256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(mlstm_prepare_kernel<float>, grid, block, 0, s, (const float*)proj, proj_stride,
+                  gates, gates_stride, bias_i, bias_f, cap, qkv, log_keep, log_in, n_heads, key_dim, value_dim);
+    else
+        cb_launch(mlstm_prepare_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)proj,
+                  proj_stride, gates, gates_stride, bias_i, bias_f, cap, qkv, log_keep, log_in, n_heads,
+                  key_dim, value_dim);
+    return cb_last_error();
+}
+
+// rule 0: the delta rule (sc0 decay, sc1 beta); rule 1: mLSTM (sc0 log keep, sc1 log in).
+CB_EXPORT int cb_matrix_memory(int rule, const float* qkv, int C, int q_off, int k_off, int v_off,
+                               const float* sc0, const float* sc1, const int* req_row_start,
+                               const int* req_state_slot, void* state, long slot_stride, long s_off,
+                               long n_off, long m_off, float* out, int n_requests, int n_heads,
+                               int n_qk_heads, int key_dim, int value_dim, void* stream) {
+    if (n_requests <= 0) return 0;
+    if (n_heads % n_qk_heads != 0) return CB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (rule == RULE_DELTA)
+        return launch_memory<RULE_DELTA>(qkv, C, q_off, k_off, v_off, sc0, sc1, req_row_start,
+                                         req_state_slot, (unsigned char*)state, slot_stride, s_off,
+                                         n_off, m_off, out, n_requests, n_heads, n_qk_heads, key_dim,
+                                         value_dim, s);
+    if (rule == RULE_MLSTM)
+        return launch_memory<RULE_MLSTM>(qkv, C, q_off, k_off, v_off, sc0, sc1, req_row_start,
+                                         req_state_slot, (unsigned char*)state, slot_stride, s_off,
+                                         n_off, m_off, out, n_requests, n_heads, n_qk_heads, key_dim,
+                                         value_dim, s);
+    return CB_ERR_UNSUPPORTED;
+}
+
+// gate_kind 0: SiLU, 1: sigmoid.
+CB_EXPORT int cb_head_norm_gate(const float* o, const float* gain, int gain_head_stride,
+                                const void* gate, int gate_stride, void* out, int out_stride, int dtype,
+                                int gate_kind, int n_rows, int n_heads, int value_dim, float eps,
+                                float out_scale, void* stream) {
+    if (n_rows <= 0) return 0;
+    const int warps = 4;
+    const long units = (long)n_rows * n_heads;
+    const dim3 grid((unsigned)((units + warps - 1) / warps)), block(warps * 32);
+    cudaStream_t s = (cudaStream_t)stream;
+#define CB_HNG(TT, GG)                                                                             \
+    cb_launch(head_norm_gate_kernel<TT, GG>, grid, block, 0, s, o, gain, gain_head_stride,         \
+              (const TT*)gate, gate_stride, (TT*)out, out_stride, n_rows, n_heads, value_dim, eps, \
+              out_scale)
+    if (dtype == CB_F32) {
+        if (gate_kind == GATE_SILU) CB_HNG(float, GATE_SILU); else CB_HNG(float, GATE_SIGMOID);
+    } else {
+        if (gate_kind == GATE_SILU) CB_HNG(__nv_bfloat16, GATE_SILU); else CB_HNG(__nv_bfloat16, GATE_SIGMOID);
+    }
+#undef CB_HNG
+    return cb_last_error();
+}

@@ -1,0 +1,216 @@
+// Paged softmax attention whose window keeps the first tokens and whose denominator
+// holds a learned sink.  Two kernels.
+//
+// (1) Preparation of a step's rows, one block per token.  A row of the joint
+//     projection is [q: H*D | k: G*D | v: G*E | ...].  Pairs (2i, 2i+1), i < R/2, of
+//     every q and k head turn by the angle position * freq[i] (the angle is an fp32
+//     product, its sine and cosine are taken in fp32); features from R on pass.
+//     q stays in the row; k goes to the token's place in the key pages; every v
+//     head is divided by its root mean square over E (eps under the root) and goes
+//     to the value pages.  Keys and values have sizes of their own (D and E):
+//     pages are [page][kv head][token][feature] for each.
+//
+// (2) Attention, one warp per (row, query head), keys one by one in ascending
+//     position with a running maximum, fp32 throughout.  A row at position p sees
+//     j <= p with p - j < window or j < keep_first, i.e. the ranges
+//     [0, min(keep_first, lo)) and [lo, p], lo = max(0, p - window + 1); window 0
+//     means every earlier key.  After the keys the sink joins the denominator:
+//     l += exp(sink[h] - m), with no value.  With a gate, the head's result is
+//     multiplied by sigmoid(gate) and by out_scale before it is stored.
+// A row's result depends on its own query and keys only.
+#define CB_PDL_BIT 10      // this file's bit in CRUCIBLE_PDL
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_PER_LANE = 8;   // key and value sizes <= 256
+
+template <typename T>
+__global__ void rotate_norm_append_kernel(T* __restrict__ proj, int proj_stride,
+                                          const float* __restrict__ freq, int rotary_dim,
+                                          const int* __restrict__ positions,
+                                          const int* __restrict__ row_request,
+                                          const int* __restrict__ block_table, int table_stride,
+                                          T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                          int n_heads, int n_kv_heads, int key_dim, int value_dim,
+                                          int page_tokens, int write_cache, float value_eps) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int t = blockIdx.x;
+    T* row = proj + (size_t)t * proj_stride;
+    const int pos = positions[t];
+    const int half = rotary_dim >> 1;
+    size_t k_base = 0, v_base = 0;
+    const size_t k_head_stride = (size_t)page_tokens * key_dim;
+    const size_t v_head_stride = (size_t)page_tokens * value_dim;
+    if (write_cache) {
+        const int page = block_table[(size_t)row_request[t] * table_stride + pos / page_tokens];
+        k_base = (size_t)page * n_kv_heads * k_head_stride + (size_t)(pos % page_tokens) * key_dim;
+        v_base = (size_t)page * n_kv_heads * v_head_stride + (size_t)(pos % page_tokens) * value_dim;
+    }
+    const int n_rot_heads = n_heads + (write_cache ? n_kv_heads : 0);
+    for (int i = threadIdx.x; i < n_rot_heads * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        T* src = row + (size_t)h * key_dim;
+        const float angle = (float)pos * freq[j];
+        float s, c;
+        sincosf(angle, &s, &c);
+        const float a = cb_to_float(src[2 * j]), b = cb_to_float(src[2 * j + 1]);
+        T* dst = h < n_heads ? src : k_cache + k_base + (size_t)(h - n_heads) * k_head_stride;
+        dst[2 * j] = cb_from_float<T>(a * c - b * s);
+        dst[2 * j + 1] = cb_from_float<T>(b * c + a * s);
+    }
+    if (!write_cache) return;
+    const int pass = key_dim - rotary_dim;
+    for (int i = threadIdx.x; i < n_kv_heads * pass; i += blockDim.x) {
+        const int h = i / pass, j = rotary_dim + (i - h * pass);
+        k_cache[k_base + (size_t)h * k_head_stride + j] = row[(size_t)(n_heads + h) * key_dim + j];
+    }
+    // values: a warp per head
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const T* v_src = row + (size_t)(n_heads + n_kv_heads) * key_dim;
+    for (int h = warp; h < n_kv_heads; h += n_warps) {
+        const T* v = v_src + (size_t)h * value_dim;
+        float ss = 0.f;
+        for (int e = lane; e < value_dim; e += 32) {
+            const float x = cb_to_float(v[e]);
+            ss = fmaf(x, x, ss);
+        }
+        const float r = 1.0f / sqrtf(cb_warp_sum(ss) / (float)value_dim + value_eps);
+        T* dst = v_cache + v_base + (size_t)h * v_head_stride;
+        for (int e = lane; e < value_dim; e += 32) dst[e] = cb_from_float<T>(cb_to_float(v[e]) * r);
+    }
+}
+
+template <typename T>
+__global__ void sink_attention_kernel(
+    const T* __restrict__ q, int q_stride, const T* __restrict__ gate, int gate_stride,
+    T* __restrict__ out, int out_stride, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+    const float* __restrict__ sinks, const int* __restrict__ positions,
+    const int* __restrict__ row_request, const int* __restrict__ block_table, int table_stride,
+    int n_rows, int n_heads, int n_kv_heads, int key_dim, int value_dim, int page_tokens,
+    float scale, int window, int keep_first, float out_scale) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int warps_per_block = blockDim.x >> 5;
+    const int unit = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    if (unit >= n_rows * n_heads) return;
+    const int lane = threadIdx.x & 31;
+    const int t = unit / n_heads, h = unit - t * n_heads;
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int pos = positions[t];
+    const int* table = block_table + (size_t)row_request[t] * table_stride;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int kept = keep_first < lo ? keep_first : lo;      // keys [0, kept) and [lo, pos]
+
+    float qv[MAX_PER_LANE], acc[MAX_PER_LANE];
+    const T* qrow = q + (size_t)t * q_stride + (size_t)h * key_dim;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+        const int f = lane + 32 * i;
+        qv[i] = f < key_dim ? cb_to_float(qrow[f]) : 0.f;
+        acc[i] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int range = 0; range < 2; ++range) {
+        const int from = range == 0 ? 0 : lo, to = range == 0 ? kept : pos + 1;
+        for (int j = from; j < to; ++j) {
+            const int page = table[j / page_tokens];
+            const size_t at = ((size_t)page * n_kv_heads + kvh) * page_tokens + (j % page_tokens);
+            const T* kp = k_cache + at * key_dim;
+            const T* vp = v_cache + at * value_dim;
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int f = lane + 32 * i;
+                if (f < key_dim) part = fmaf(qv[i], cb_to_float(kp[f]), part);
+            }
+            const float s = cb_warp_sum(part) * scale;
+            const float m_new = fmaxf(m, s);
+            const float corr = expf(m - m_new);
+            const float p = expf(s - m_new);
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int f = lane + 32 * i;
+                if (f < value_dim) acc[i] = fmaf(p, cb_to_float(vp[f]), acc[i] * corr);
+            }
+            m = m_new;
+        }
+    }
+    float corr = 1.f;
+    if (sinks != nullptr) {
+        const float sk = sinks[h];
+        const float m_new = fmaxf(m, sk);
+        corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+    }
+    const float inv = corr / l;
+    T* orow = out + (size_t)t * out_stride + (size_t)h * value_dim;
+    const T* grow = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * value_dim : nullptr;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+        const int f = lane + 32 * i;
+        if (f < value_dim) {
+            float o = acc[i] * inv;
+            if (grow != nullptr) o *= 1.0f / (1.0f + expf(-cb_to_float(grow[f])));
+            orow[f] = cb_from_float<T>(o * out_scale);
+        }
+    }
+}
+
+}  // namespace
+
+CB_EXPORT int cb_rotate_norm_append(void* proj, int proj_stride, int dtype, const float* freq,
+                                    int rotary_dim, const int* positions, const int* row_request,
+                                    const int* block_table, int table_stride, void* k_cache,
+                                    void* v_cache, int n_rows, int n_heads, int n_kv_heads, int key_dim,
+                                    int value_dim, int page_tokens, int write_cache, float value_eps,
+                                    void* stream) {
+    if (n_rows <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > key_dim || (rotary_dim & 1)) return CB_ERR_UNSUPPORTED;
+    int threads = ((n_heads + n_kv_heads) * (rotary_dim / 2) + 31) / 32 * 32;
+    threads = threads > 256 ? 256 : (threads < 64 ? 64 : threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(rotate_norm_append_kernel<float>, dim3(n_rows), dim3(threads), 0, s, (float*)proj,
+                  proj_stride, freq, rotary_dim, positions, row_request, block_table, table_stride,
+                  (float*)k_cache, (float*)v_cache, n_heads, n_kv_heads, key_dim, value_dim,
+                  page_tokens, write_cache, value_eps);
+    else
+        cb_launch(rotate_norm_append_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s,
+                  (__nv_bfloat16*)proj, proj_stride, freq, rotary_dim, positions, row_request,
+                  block_table, table_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads,
+                  n_kv_heads, key_dim, value_dim, page_tokens, write_cache, value_eps);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_sink_attention(const void* q, int q_stride, const void* gate, int gate_stride,
+                                void* out, int out_stride, const void* k_cache, const void* v_cache,
+                                int dtype, const float* sinks, const int* positions,
+                                const int* row_request, const int* block_table, int table_stride,
+                                int n_rows, int n_heads, int n_kv_heads, int key_dim, int value_dim,
+                                int page_tokens, float scale, int window, int keep_first,
+                                float out_scale, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (key_dim > 32 * MAX_PER_LANE || value_dim > 32 * MAX_PER_LANE || n_heads % n_kv_heads != 0)
+        return CB_ERR_UNSUPPORTED;
+    const int warps = 4;
+    const long units = (long)n_rows * n_heads;
+    const int blocks = (int)((units + warps - 1) / warps);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(sink_attention_kernel<float>, dim3(blocks), dim3(warps * 32), 0, s, (const float*)q,
+                  q_stride, (const float*)gate, gate_stride, (float*)out, out_stride,
+                  (const float*)k_cache, (const float*)v_cache, sinks, positions, row_request,
+                  block_table, table_stride, n_rows, n_heads, n_kv_heads, key_dim, value_dim,
+                  page_tokens, scale, window, keep_first, out_scale);
+    else
+        cb_launch(sink_attention_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, s,
+                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)gate, gate_stride,
+                  (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_cache,
+                  (const __nv_bfloat16*)v_cache, sinks, positions, row_request, block_table,
+                  table_stride, n_rows, n_heads, n_kv_heads, key_dim, value_dim, page_tokens, scale,
+                  window, keep_first, out_scale);
+    return cb_last_error();
+}

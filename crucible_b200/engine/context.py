@@ -54,19 +54,29 @@ class CacheStorage:
     elements in a row), so a head's keys are read in long runs."""
 
     def __init__(self, n_slots: int, n_pages: int, page_tokens: int, kv_heads: int,
-                 head_dim: int, dtype: torch.dtype, device):
+                 head_dim: int, dtype: torch.dtype, device, value_dim: Optional[int] = None):
         self.page_tokens = page_tokens
         self.n_pages = n_pages
         self.kv_heads = kv_heads
         self.head_dim = head_dim
-        self.kv = torch.zeros((n_slots, 2, n_pages, kv_heads, page_tokens, head_dim),
-                              dtype=dtype, device=device)
+        self.value_dim = head_dim if value_dim is None else value_dim
+        if self.value_dim == head_dim:
+            self.kv = torch.zeros((n_slots, 2, n_pages, kv_heads, page_tokens, head_dim),
+                                  dtype=dtype, device=device)
+            self._k = self._v = None
+        else:
+            # values of a size of their own: the same page ids, pages of another size
+            self.kv = None
+            self._k = torch.zeros((n_slots, n_pages, kv_heads, page_tokens, head_dim),
+                                  dtype=dtype, device=device)
+            self._v = torch.zeros((n_slots, n_pages, kv_heads, page_tokens, self.value_dim),
+                                  dtype=dtype, device=device)
 
     def keys(self, slot: int) -> torch.Tensor:
-        return self.kv[slot, 0]
+        return self.kv[slot, 0] if self.kv is not None else self._k[slot]
 
     def values(self, slot: int) -> torch.Tensor:
-        return self.kv[slot, 1]
+        return self.kv[slot, 1] if self.kv is not None else self._v[slot]
 
 
 class Scratch:

@@ -95,6 +95,8 @@ class EngineOptions:
     device: str = "cuda:0"
     graph: bool = True                    # replay decode-only steps as CUDA graphs
     profile: bool = False                 # CUDA events around every part's forward; steps run eagerly
+    max_context: Optional[int] = None     # most tokens of a request; default: the model's limit, or,
+                                          # for a design that names none, what the page pool holds
 
 
 class Engine:
@@ -122,7 +124,16 @@ class Engine:
         o = self.options
         if o.page_tokens <= 0:
             raise ValueError("page_tokens must be positive")
-        ctx_pages = -(-self.config.max_context // o.page_tokens)
+        from ..config.model_config import UNBOUNDED_CONTEXT
+        limit = self.config.max_context
+        if o.max_context is not None:
+            limit = min(limit, int(o.max_context))
+        elif limit >= UNBOUNDED_CONTEXT:
+            limit = o.n_pages * o.page_tokens if o.n_pages is not None else 8192
+        if limit <= 0:
+            raise ValueError("max_context must be positive")
+        self.context_limit = limit
+        ctx_pages = -(-limit // o.page_tokens)
         n_pages = o.n_pages if o.n_pages is not None else o.max_requests * ctx_pages
         groups = self.model.cache_groups
         # One page more than the pool hands out: the null page, never written, all zeros.
@@ -130,7 +141,8 @@ class Engine:
         # kernel that loads whole tiles of keys reads zeros there (every such key is masked)
         # and never another request's data.
         self.storages = [CacheStorage(len(g.layers), n_pages + 1, o.page_tokens, g.need.kv_heads,
-                                      g.need.head_dim, self.dtype, self.device) for g in groups]
+                                      g.need.head_dim, self.dtype, self.device,
+                                      value_dim=g.need.value_dim) for g in groups]
         self.null_page = n_pages
         self.table_strides = tuple(ctx_pages for _ in groups)
         # The manager keeps every live request's table in the form that goes to the device
@@ -139,7 +151,7 @@ class Engine:
         # refused before anything is written (`engine/src/gpu_model.rs:2809-2934` refuses
         # such a batch).
         self.cache = CacheManager(
-            [GroupPolicy(o.page_tokens, g.need.window) for g in groups],
+            [GroupPolicy(o.page_tokens, g.need.window, g.need.keep_first) for g in groups],
             [n_pages] * len(groups), o.max_requests, table_strides=self.table_strides,
             null_pages=[self.null_page] * len(groups))
         self._has_device_token = set()      # state slots whose latest token is on the device
@@ -216,7 +228,7 @@ class Engine:
 
     @property
     def max_context(self) -> int:
-        return self.config.max_context
+        return self.context_limit
 
     @property
     def max_device_top_k(self) -> int:
@@ -307,7 +319,7 @@ class Engine:
             # every request's pages for this step, or nobody's; the tables that will go to
             # the device come back as the addresses of the manager's rows
             code = cache.step_raw(n_req, ints[2].ctypes.data, ints[0].ctypes.data,
-                                  self.config.max_context, ints[1].ctypes.data, rows)
+                                  self.context_limit, ints[1].ctypes.data, rows)
             if code:
                 who = entries[cache.failed_entry()].request
                 if code in (cache_codes.TOO_LONG, cache_codes.ALIASED):
@@ -466,9 +478,9 @@ class Engine:
                     raise StepError(f"request {e.request!r} has no token on the device yet")
             if not known:
                 new_requests += 1
-                if n > self.config.max_context:
+                if n > self.context_limit:
                     raise StepError(f"request {e.request!r} would hold {n} tokens; the "
-                                    f"model's context is {self.config.max_context}")
+                                    f"model's context is {self.context_limit}")
         if new_requests and new_requests > cache.slots.free_slots:
             raise StepError(f"{new_requests} new requests but only "
                             f"{cache.slots.free_slots} of {self.options.max_requests} "
@@ -511,7 +523,7 @@ class Engine:
         code = pack.fn(host_t.data_ptr(), n_req, ints[0].ctypes.data, ints[1].ctypes.data,
                        ints[2].ctypes.data, tokens.ctypes.data, ints[3].ctypes.data,
                        wants.ctypes.data, n_groups, pack.strides, rows, self.config.vocab_size,
-                       self.config.max_context, DEVICE_TOKEN, ctypes.byref(bad), pack.err, 256)
+                       self.context_limit, DEVICE_TOKEN, ctypes.byref(bad), pack.err, 256)
         if code != 0:
             who = entries[bad.value].request if 0 <= bad.value < n_req else None
             raise StepError(f"request {who!r}: {pack.err.value.decode()}")

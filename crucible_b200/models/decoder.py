@@ -124,6 +124,8 @@ class DecoderModel:
                 yield f"layer.{name}", norm, li
             yield "layer.mixer", layer.mixer, li
             yield "layer.feed_forward", layer.feed_forward, li
+            if hasattr(layer, "tensors"):          # an arrangement with weights of its own
+                yield "layer.arrangement", layer, li
 
     def tensor_requests(self) -> List[TensorRequest]:
         names = self.config.tensor_names
@@ -188,7 +190,13 @@ class DecoderModel:
         ctx.norm_after_layer = None
         if ctx.n_logit_rows == 0:
             return ctx.scratch("logits", (0, self.config.vocab_size), torch.float32)
-        if ctx.host.all_single_token and ctx.n_logit_rows == ctx.n_tokens:
+        if x.dim() == 3:
+            # a residual of several streams: the model's result is their sum
+            from ..ops import streams
+            rows = ctx.scratch("head.rows", (ctx.n_logit_rows, self.config.hidden_size),
+                               torch.float32)
+            streams.sum_rows(x, ctx.logit_rows, rows)
+        elif ctx.host.all_single_token and ctx.n_logit_rows == ctx.n_tokens:
             # every request brings one token and wants its logits: the wanted rows are the
             # step's rows in order (a fact of the step's shape, so a captured step replays)
             rows = x

@@ -108,6 +108,20 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                          _c_int(out.shape[0]), _c_int(out.shape[1]), _stream()), "swiglu")
 
 
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps);
+    `coef` = (a, b, c, e) in float32."""
+    _need_cuda(z, coef, out)
+    if z.dtype != out.dtype or z.shape != out.shape or coef.dtype != torch.float32 or coef.numel() != 4:
+        raise KernelError("polynorm takes [T, F] rows, writes the same, and four float32 numbers")
+    if z.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("polynorm: rows must be contiguous")
+    lib = build.load("polynorm")
+    _check(lib.cb_polynorm(_ptr(z), _c_int(z.stride(0)), _ptr(coef), _ptr(out), _c_int(out.stride(0)),
+                           _c_int(_code(z.dtype)), _c_int(z.shape[0]), _c_int(z.shape[1]),
+                           _c_float(eps), _stream()), "polynorm")
+
+
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
     _need_cuda(x, rows, out)
     if x.dtype != torch.float32 or out.dtype != torch.float32 or rows.dtype != torch.int32:

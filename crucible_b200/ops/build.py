@@ -42,6 +42,10 @@ MODULES: Dict[str, List[str]] = {
     "gemm_simt": ["common.cuh"],
     "attention_generic": ["common.cuh"],
     "sampling": ["common.cuh", "no_alloc_argmax.h"],
+    "streams": ["common.cuh"],
+    "sink_attention": ["common.cuh"],
+    "recurrent": ["common.cuh"],
+    "polynorm": ["common.cuh"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

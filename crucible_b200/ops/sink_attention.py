@@ -1,0 +1,59 @@
+"""Wrappers of `csrc/sink_attention.cu`: attention whose window keeps the first
+tokens and whose softmax has a sink; keys and values of sizes of their own."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import KernelError, _c_float, _c_int, _check, _code, _need_cuda, _ptr, _stream, build
+
+
+def rotate_norm_append(proj: torch.Tensor, freq: Optional[torch.Tensor], rotary_dim: int,
+                       n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int,
+                       value_eps: float, ctx, cache, binding) -> None:
+    """Rows of `proj` are [q | k | v | ...]: q and k turn by position * freq (interleaved
+    pairs), q in place; k and the unit-rms v go to the token's place in the pages."""
+    _need_cuda(proj, freq)
+    if proj.stride(1) != 1:
+        raise KernelError("rotate_norm_append: rows must be contiguous")
+    if rotary_dim and (freq is None or freq.dtype != torch.float32 or freq.numel() * 2 != rotary_dim):
+        raise KernelError("rotate_norm_append: freq is float32 [rotary_dim / 2]")
+    k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
+    if k_cache.dtype != proj.dtype:
+        raise KernelError("rotate_norm_append: cache dtype differs from the activations'")
+    if k_cache.shape[-1] != key_dim or v_cache.shape[-1] != value_dim:
+        raise KernelError("rotate_norm_append: the pages' sizes differ from the heads'")
+    table = ctx.block_table(binding.group)
+    lib = build.load("sink_attention")
+    _check(lib.cb_rotate_norm_append(
+        _ptr(proj), _c_int(proj.stride(0)), _c_int(_code(proj.dtype)), _ptr(freq), _c_int(rotary_dim),
+        _ptr(ctx.positions), _ptr(ctx.row_request), _ptr(table), _c_int(table.shape[1]),
+        _ptr(k_cache), _ptr(v_cache), _c_int(proj.shape[0]), _c_int(n_heads), _c_int(n_kv_heads),
+        _c_int(key_dim), _c_int(value_dim), _c_int(cache.page_tokens),
+        _c_int(1 if binding.write else 0), _c_float(value_eps), _stream()), "rotate_norm_append")
+
+
+def attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
+              sinks: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, key_dim: int,
+              value_dim: int, scale: float, window: Optional[int], keep_first: int,
+              out_scale: float, ctx, cache, binding) -> None:
+    """`q`, `gate`, `out`: views of rows (unit stride along features).  Position p sees
+    j <= p with p - j < window or j < keep_first.  out = softmax-with-sink(q k) v, times
+    sigmoid(gate) if given, times out_scale."""
+    _need_cuda(q, gate, out, sinks)
+    for t in (q, gate, out):
+        if t is not None and t.stride(1) != 1:
+            raise KernelError("sink attention: rows must be contiguous along features")
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads):
+        raise KernelError("sink attention: one float32 sink per query head")
+    k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
+    table = ctx.block_table(binding.group)
+    lib = build.load("sink_attention")
+    _check(lib.cb_sink_attention(
+        _ptr(q), _c_int(q.stride(0)), _ptr(gate), _c_int(gate.stride(0) if gate is not None else 0),
+        _ptr(out), _c_int(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _c_int(_code(q.dtype)),
+        _ptr(sinks), _ptr(ctx.positions), _ptr(ctx.row_request), _ptr(table), _c_int(table.shape[1]),
+        _c_int(q.shape[0]), _c_int(n_heads), _c_int(n_kv_heads), _c_int(key_dim), _c_int(value_dim),
+        _c_int(cache.page_tokens), _c_float(scale), _c_int(window or 0), _c_int(keep_first),
+        _c_float(out_scale), _stream()), "sink attention")

@@ -48,6 +48,9 @@ class TensorDecl:
     shape: Tuple[int, ...]
     role: str = "matrix"
     optional: bool = False         # absent tensors of optional decls are passed as None
+    # how the random-weights mode draws it, if not by its role's rule: ("normal", mean, std),
+    # ("uniform", low, high) or ("eye", diagonal, std of the noise around it)
+    init: Optional[Tuple[str, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -56,6 +59,8 @@ class CacheNeed:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None   # None: every earlier key stays
+    value_dim: Optional[int] = None   # size of a value, if it differs from a key's
+    keep_first: int = 0            # with a window: this many first tokens stay visible
 
 
 @dataclass(frozen=True)

@@ -34,6 +34,34 @@ class TokenEmbedding(Embedding):
         return x
 
 
+class NormedStreamsEmbedding(Embedding):
+    """x0 = rmsnorm(table[token]) * gain, copied into every one of `streams` residual
+    streams: fp32 [T, streams, width] (or [T, width] when `streams` is None)."""
+
+    def __init__(self, spec, vocab_size: int, width: int):
+        self.vocab_size = vocab_size
+        self.width = width
+        self.eps = float(spec.option("eps", 1e-6))
+        self.streams = spec.option("streams")
+        self.table = self.gain = None
+
+    def tensors(self):
+        return [TensorDecl("table", (self.vocab_size, self.width)),
+                TensorDecl("norm_gain", (self.width,), role="vector")]
+
+    def bind(self, tensors, dtype, device):
+        self.table, self.gain = tensors["table"], tensors["norm_gain"]
+        ops.declare_weights(self.table)
+
+    def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
+        from ..ops import streams
+        n = int(self.streams or 1)
+        x = ctx.scratch("residual", (token_ids.shape[0], n, self.width), torch.float32)
+        streams.embed_norm(self.table, token_ids, self.gain, self.eps, x,
+                           getattr(ctx, "device_tokens", None))
+        return x if self.streams is not None else x.view(token_ids.shape[0], self.width)
+
+
 class LMHead(Head):
     def __init__(self, vocab_size: int, width: int, tied: bool):
         self.vocab_size = vocab_size
@@ -59,4 +87,5 @@ class LMHead(Head):
 
 
 EMBEDDINGS.register("token", lambda spec, vocab, width: TokenEmbedding(vocab, width))
+EMBEDDINGS.register("token_normed_streams", NormedStreamsEmbedding)
 HEADS.register("linear", lambda spec, vocab, width, tied: LMHead(vocab, width, tied))

@@ -50,3 +50,28 @@ class RotaryEncoding(PositionEncoding):
 
 
 POSITIONS.register("rope", RotaryEncoding)
+
+
+class InterleavedRotary(PositionEncoding):
+    """Rotation of neighbouring pairs: features (2i, 2i+1), i < rotary_dim / 2, of a head
+    turn by the angle position * theta^(-2i / rotary_dim); features from rotary_dim on
+    pass unchanged.  (u, v) -> (u cos a - v sin a, v cos a + u sin a).  The frequencies
+    are float32 numbers and the angle is a float32 product taken in the kernel, so there
+    is no table over positions and no longest position."""
+
+    def __init__(self, spec: PositionSpec):
+        if spec.rotary_dim % 2 != 0 or spec.rotary_dim < 0:
+            raise ValueError(f"rotary_dim must be even and not negative, got {spec.rotary_dim}")
+        self.spec = spec
+        self.freq = None
+
+    def bind(self, tensors, dtype, device):
+        n = self.spec.rotary_dim
+        i = torch.arange(n // 2, dtype=torch.float32)
+        self.freq = (float(self.spec.theta) ** (-2.0 * i / n)).to(torch.float32).to(device) if n else None
+
+    def frequencies(self):
+        return self.freq, self.spec.rotary_dim
+
+
+POSITIONS.register("rope_interleaved", InterleavedRotary)
