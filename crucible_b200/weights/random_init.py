@@ -34,7 +34,22 @@ def random_tensors(model, seed: int, std: float = 0.02,
                    store_dtype: torch.dtype = torch.bfloat16) -> dict:
     out = {}
     for r in model.tensor_requests():
-        if r.decl.role == "vector":
+        if r.decl.init is not None and r.decl.role != "int_table":
+            # the part's own rule (gates, mixing weights, taps: numbers for which neither
+            # "all ones" nor N(0, std) gives a model that runs sensibly)
+            g = torch.Generator(device="cpu").manual_seed(_tensor_seed(seed, r.checkpoint_name))
+            kind, a, b = r.decl.init
+            if kind == "normal":
+                t = a + b * torch.randn(r.decl.shape, generator=g, dtype=torch.float32)
+            elif kind == "uniform":
+                t = a + (b - a) * torch.rand(r.decl.shape, generator=g, dtype=torch.float32)
+            elif kind == "eye":
+                t = a * torch.eye(*r.decl.shape, dtype=torch.float32) \
+                    + b * torch.randn(r.decl.shape, generator=g, dtype=torch.float32)
+            else:
+                raise ValueError(f"{r.checkpoint_name}: unknown init rule {kind!r}")
+            out[r.checkpoint_name] = t.to(store_dtype)
+        elif r.decl.role == "vector":
             out[r.checkpoint_name] = torch.ones(r.decl.shape, dtype=torch.float32)
         elif r.decl.role == "int_table":
             out[r.checkpoint_name] = torch.zeros(r.decl.shape, dtype=torch.int32)

@@ -51,6 +51,30 @@ def visible(i, j, size, keep_first):
     return j <= i and (i - j < size or j < keep_first)
 
 
+def attend(q, k, v, positions, sink, scale, size, keep_first):
+    """q: [T, H, D], k: [T, G, D], v: [T, G, E] of one sequence at `positions` (already
+    turned and normalised); sink: [H] or None; size None: every earlier key.
+    Returns [T, H, E]."""
+    T, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    allowed = torch.tensor([[visible(int(i), int(j), size if size is not None else 1 << 60, keep_first)
+                             for j in positions] for i in positions])
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for head in range(H):
+        g = head // (H // G)
+        s = (q[:, head] @ k[:, g].T) * scale
+        s = s.masked_fill(~allowed, float("-inf"))
+        m = s.max(-1).values
+        if sink is not None:
+            m = torch.maximum(m, sink[head])
+        e = torch.exp(s - m[:, None])
+        denom = e.sum(-1)
+        if sink is not None:
+            denom = denom + torch.exp(sink[head] - m)
+        out[:, head] = (e / denom[:, None]) @ v[:, g]
+    return out
+
+
 def sink_window_attention(h, w, cfg, eps, prefix=""):
     """Softmax attention with grouped heads, a window that keeps the first tokens, a
     per-head sink in the denominator, unit-rms values and a sigmoid output gate.
@@ -61,21 +85,13 @@ def sink_window_attention(h, w, cfg, eps, prefix=""):
     k = (h @ w[prefix + "k"].T).view(T, G, D)
     v = (h @ w[prefix + "v"].T).view(T, G, E)
     pos = torch.arange(T)
-    q = rotate_interleaved(q, pos, cfg["rot"]["base"], cfg["rot"]["dims"])
-    k = rotate_interleaved(k, pos, cfg["rot"]["base"], cfg["rot"]["dims"])
+    if cfg.get("rot") is not None:
+        q = rotate_interleaved(q, pos, cfg["rot"]["base"], cfg["rot"]["dims"])
+        k = rotate_interleaved(k, pos, cfg["rot"]["base"], cfg["rot"]["dims"])
     v = rms_unit(v, eps)
-    size, keep = cfg["mask"]["size"], cfg["mask"]["keep_first"]
-    allowed = torch.tensor([[visible(i, j, size, keep) for j in range(T)] for i in range(T)])
-    out = torch.zeros(T, H, E, dtype=h.dtype)
-    for head in range(H):
-        g = head // (H // G)
-        s = (q[:, head] @ k[:, g].T) * cfg["scale"]
-        s = s.masked_fill(~allowed, float("-inf"))
-        sink = w[prefix + "sink"][head]
-        m = torch.maximum(s.max(-1).values, sink)
-        e = torch.exp(s - m[:, None])
-        denom = e.sum(-1) + torch.exp(sink - m)
-        out[:, head] = (e / denom[:, None]) @ v[:, g]
+    mask = cfg.get("mask")
+    out = attend(q, k, v, pos, w[prefix + "sink"], cfg["scale"],
+                 mask["size"] if mask else None, mask.get("keep_first", 0) if mask else 0)
     gate = torch.sigmoid(h @ w[prefix + "g"].T)
     return (out.reshape(T, H * E) * gate) @ w[prefix + "o"].T
 
@@ -90,6 +106,20 @@ def causal_conv(x, taps_w):
     for j in range(taps):
         out = out + padded[j:j + T] * taps_w[:, j][None, :]
     return out
+
+
+def delta_rule(q, k, v, beta, decay, S=None):
+    """One head.  q, k: [T, D] (unit vectors, q scaled), v: [T, E], beta, decay: [T].
+    S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  Returns (o [T, E], S)."""
+    T, D = q.shape
+    S = torch.zeros(D, v.shape[1], dtype=q.dtype) if S is None else S.clone()
+    out = torch.zeros(T, v.shape[1], dtype=q.dtype)
+    for t in range(T):
+        S = decay[t] * S
+        u = beta[t] * (v[t] - S.T @ k[t])
+        S = S + torch.outer(k[t], u)
+        out[t] = S.T @ q[t]
+    return out, S
 
 
 def gated_delta(h, w, cfg, eps, prefix=""):
@@ -107,12 +137,7 @@ def gated_delta(h, w, cfg, eps, prefix=""):
     out = torch.zeros(T, H, E, dtype=h.dtype)
     for head in range(H):
         g = head // (H // G)
-        S = torch.zeros(D, E, dtype=h.dtype)
-        for t in range(T):
-            S = decay[t, head] * S
-            u = beta[t, head] * (v[t, head] - S.T @ k[t, g])
-            S = S + torch.outer(k[t, g], u)
-            out[t, head] = S.T @ q[t, g]
+        out[:, head], _ = delta_rule(q[:, g], k[:, g], v[:, head], beta[:, head], decay[:, head])
     out = rms_unit(out, eps) * w[prefix + "norm"]
     gate = silu(h @ w[prefix + "g"].T).view(T, H, E)
     return (out * gate).reshape(T, H * E) @ w[prefix + "o"].T
@@ -124,6 +149,31 @@ def parallel_mixer(h, w, cfg, eps):
     return cfg["left_scale"] * left + cfg["right_scale"] * right
 
 
+def matrix_memory(q, k, v, log_in, log_keep):
+    """One head of the mLSTM.  q (scaled), k: [T, D], v: [T, E], log gates [T].  The
+    running maximum starts at zero.  Returns o [T, E]."""
+    T, D = q.shape
+    S = torch.zeros(D, v.shape[1], dtype=q.dtype)
+    n = torch.zeros(D, dtype=q.dtype)
+    m = torch.zeros((), dtype=q.dtype)
+    out = torch.zeros(T, v.shape[1], dtype=q.dtype)
+    for t in range(T):
+        m_new = torch.maximum(log_keep[t] + m, log_in[t])
+        a = torch.exp(log_keep[t] + m - m_new)
+        b = torch.exp(log_in[t] - m_new)
+        S = a * S + b * torch.outer(k[t], v[t])
+        n = a * n + b * k[t]
+        m = m_new
+        out[t] = (S.T @ q[t]) / (torch.maximum((n @ q[t]).abs(), torch.exp(-m)) + 1e-6)
+    return out
+
+
+def capped_log_gates(pre_i, pre_f, cap):
+    log_in = cap * torch.tanh(pre_i / cap)
+    log_keep = torch.nn.functional.logsigmoid(cap * torch.tanh(pre_f / cap))
+    return log_in, log_keep
+
+
 def mlstm(h, w, cfg, eps):
     """Matrix memory with exponential gates kept stable by a running maximum that
     starts at zero."""
@@ -132,31 +182,31 @@ def mlstm(h, w, cfg, eps):
     q = (h @ w["q"].T).view(T, H, D) * D ** -0.5
     k = (h @ w["k"].T).view(T, H, D)
     v = (h @ w["v"].T).view(T, H, E)
-    log_in = cap * torch.tanh((h @ w["i"].T + w["i.b"]) / cap)
-    log_keep = torch.nn.functional.logsigmoid(cap * torch.tanh((h @ w["f"].T + w["f.b"]) / cap))
+    log_in, log_keep = capped_log_gates(h @ w["i"].T + w["i.b"], h @ w["f"].T + w["f.b"], cap)
     out = torch.zeros(T, H, E, dtype=h.dtype)
     for head in range(H):
-        S = torch.zeros(D, E, dtype=h.dtype)
-        n = torch.zeros(D, dtype=h.dtype)
-        m = torch.zeros((), dtype=h.dtype)
-        for t in range(T):
-            m_new = torch.maximum(log_keep[t, head] + m, log_in[t, head])
-            a = torch.exp(log_keep[t, head] + m - m_new)
-            b = torch.exp(log_in[t, head] - m_new)
-            S = a * S + b * torch.outer(k[t, head], v[t, head])
-            n = a * n + b * k[t, head]
-            m = m_new
-            denom = torch.maximum((n @ q[t, head]).abs(), torch.exp(-m)) + 1e-6
-            out[t, head] = (S.T @ q[t, head]) / denom
+        out[:, head] = matrix_memory(q[:, head], k[:, head], v[:, head], log_in[:, head],
+                                     log_keep[:, head])
     out = rms_unit(out, eps).reshape(T, H * E) * w["norm"]
     return (out * torch.sigmoid(h @ w["g"].T)) @ w["o"].T
 
 
+def polynorm(z, coef, eps):
+    a, b, c, e = coef
+    return a * rms_unit(z, eps) + b * rms_unit(z ** 2, eps) + c * rms_unit(z ** 3, eps) + e
+
+
 def polynorm_ff(h, w, eps):
-    z = h @ w["up"].T
-    a, b, c, e = w["act"]
-    act = a * rms_unit(z, eps) + b * rms_unit(z ** 2, eps) + c * rms_unit(z ** 3, eps) + e
-    return act @ w["down"].T
+    return polynorm(h @ w["up"].T, w["act"], eps) @ w["down"].T
+
+
+def hyper_sublayer(streams, y_of, gain, eps, w_in, w_mix, w_out):
+    """streams: list of [T, W].  u = sum_s in[s] x_s; y = y_of(norm(u));
+    x_t <- sum_s mix[s, t] x_s + out[t] y, all t from the old streams."""
+    n = len(streams)
+    u = sum(w_in[s] * streams[s] for s in range(n))
+    y = y_of(rms_norm(u, gain, eps))
+    return [sum(w_mix[s, t] * streams[s] for s in range(n)) + w_out[t] * y for t in range(n)]
 
 
 def sub(tensors, prefix):
@@ -177,10 +227,7 @@ def forward(config, tensors, tokens, dtype=torch.float64, layer_outputs=None):
         if n_streams is None:
             streams = [streams[0] + fn(rms_norm(streams[0], norm_gain, eps))]
             return
-        u = sum(hc["in"][s] * streams[s] for s in range(n_streams))
-        y = fn(rms_norm(u, norm_gain, eps))
-        streams = [sum(hc["mix"][s, t] * streams[s] for s in range(n_streams)) + hc["out"][t] * y
-                   for t in range(n_streams)]
+        streams = hyper_sublayer(streams, fn, norm_gain, eps, hc["in"], hc["mix"], hc["out"])
 
     for li, layer in enumerate(config["layers"]):
         lw = sub(w, f"l{li}.")
@@ -199,3 +246,25 @@ def forward(config, tensors, tokens, dtype=torch.float64, layer_outputs=None):
             layer_outputs.append(sum(streams))
     x = rms_norm(sum(streams), w["final.norm"], eps)
     return x @ w["embed"].T
+
+
+def read_folder(model_dir, dtype=torch.float64):
+    """(config.json as a dict, tensors by name) of a model folder."""
+    import json
+    import os
+    from safetensors import safe_open
+    with open(os.path.join(model_dir, "config.json")) as f:
+        config = json.load(f)
+    tensors = {}
+    with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            t = f.get_tensor(name)
+            tensors[name] = t.to(dtype) if t.is_floating_point() else t
+    return config, tensors
+
+
+def greedy(config, tensors, prompt, n_new):
+    tokens = list(prompt)
+    for _ in range(n_new):
+        tokens.append(int(forward(config, tensors, tokens)[-1].argmax()))
+    return tokens[len(prompt):]
