@@ -618,6 +618,76 @@ def run_profile_case(args):
     return 0
 
 
+def run_design_comparison(args):
+    """`--compare vuvosun`: prefill and decode throughput of the Vuvosun design at a few sizes
+    of a real model's proportions (random weights), beside the dense Llama-style decoder at
+    equal width, layers, heads, feed-forward width and vocabulary; and, from one eager
+    prompt step and one eager decode step each, the device time of every kind of launch."""
+    import torch
+    from crucible_b200 import ops
+    from crucible_b200.config import parse_config
+    from crucible_b200.config.presets import COMPARISON_SIZES, _llama, vuvosun
+    from crucible_b200.engine import Engine, EngineOptions, StepEntry
+    from crucible_b200.weights import write_random_model
+    peaks = read_peaks()
+    rng = random.Random(1)
+    t_prefill, ctx_len, batch, layers = 2048, args.context, args.batch, args.layers or 4
+    out = {"compare": "vuvosun", "dtype": "bf16", "data": "synthetic", "layers": layers,
+           "prefill_tokens": t_prefill, "decode_batch": batch, "decode_context": ctx_len,
+           "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops")}, "sizes": {}}
+    for label, (width, heads, kv, hd, ff, vocab) in COMPARISON_SIZES.items():
+        raws = {"vuvosun": vuvosun(width, heads, kv, hd, ff, vocab, layers=layers),
+                "llama": _llama(vocab, layers, heads, kv, width, hd, ff, 8192, 10000.0, 1e-5, True)}
+        row = {}
+        for design, raw in raws.items():
+            pages = (batch + 1) * (-(-(ctx_len + args.steps + args.warmup + 64) // 16)) + 256
+            res = {}
+            for graph in (True, False):
+                with tempfile.TemporaryDirectory() as tmp:
+                    folder = write_random_model(raw, os.path.join(tmp, "m"), seed=0)
+                    engine = Engine(folder, EngineOptions(dtype="bfloat16", page_tokens=16, n_pages=pages,
+                                                          max_requests=batch + 1, graph=graph,
+                                                          max_context=ctx_len + args.steps + args.warmup + 64))
+                toks = lambda n: [rng.randrange(vocab) for _ in range(n)]
+                ids = [f"d{i}" for i in range(batch)]
+
+                def prefill():
+                    engine.step([StepEntry("p", toks(t_prefill), [t_prefill - 1])])
+                    engine.finish("p")
+
+                def decode():
+                    engine.step([StepEntry(rid, [rng.randrange(vocab)], [0]) for rid in ids])
+                for _ in range(3):
+                    prefill()
+                for rid in ids:
+                    engine.step([StepEntry(rid, toks(ctx_len - 1), [])])
+                for _ in range(args.warmup):
+                    decode()
+                if graph:
+                    for name, fn, n, tokens in (("prefill", prefill, 6, t_prefill),
+                                                ("decode", decode, args.steps, batch)):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        torch.cuda.synchronize()
+                        e0.record()
+                        for _ in range(n):
+                            fn()
+                        e1.record()
+                        torch.cuda.synchronize()
+                        ms = e0.elapsed_time(e1) / n
+                        res[name] = {"ms": round(ms, 4), "tok_s": round(tokens / (ms / 1e3), 1)}
+                else:
+                    for name, fn in (("prefill", prefill), ("decode", decode)):
+                        table = ops.timed_launches(fn)
+                        res[name + "_launches"] = {k: [round(ms, 4), n] for k, (ms, n) in
+                                                   sorted(table.items(), key=lambda kv: -kv[1][0])}
+                del engine
+                torch.cuda.empty_cache()
+            row[design] = res
+        out["sizes"][label] = row
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -632,7 +702,14 @@ def main():
                    help="fewer layers than the shape has (both numbers are reported)")
     p.add_argument("--profile-case", default=None, choices=["prefill", "decode"],
                    help="run a small eager workload for a profiler instead of the benchmark")
+    p.add_argument("--compare", default=None, choices=["vuvosun"],
+                   help="instead of the benchmark: this design beside the dense decoder at equal sizes")
     args = p.parse_args()
+    if args.compare:
+        if args.steps == 256:
+            args.steps = 64
+        args.warmup = max(args.warmup, 3)
+        return run_design_comparison(args)
     if args.profile_case:
         return run_profile_case(args)
     if args.gpus != 1:

@@ -44,3 +44,24 @@ def shape(name: str) -> dict:
         return dict(SHAPES[name])
     except KeyError:
         raise KeyError(f"unknown shape {name!r}; known: {sorted(SHAPES)}") from None
+
+
+def vuvosun(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int,
+            layers: int = 4, window: int = 1024, keep_first: int = 4, streams: int = 4) -> dict:
+    """A Vuvosun config.json of a real model's proportions: `layers` layers that alternate
+    mLSTM (no feed-forward) and parallel attention + delta rule (dense feed-forward), every
+    mixer `heads * head_dim` wide."""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+            "scale": head_dim ** -0.5, "rot": {"base": 10000.0, "dims": head_dim // 2},
+            "mask": {"size": window, "keep_first": keep_first}}
+    right = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "conv": 4}
+    parallel = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff},
+                "mixer": {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.7}}
+    mlstm = {"type": "mlstm", "mlp": None,
+             "mixer": {"heads": heads, "dim": head_dim, "vdim": head_dim, "gate_cap": 15.0}}
+    return {"architecture": "Vuvosun", "vocab": vocab, "width": width, "streams": streams,
+            "norm": {"eps": 1e-5}, "layers": [mlstm if i % 2 == 0 else parallel for i in range(layers)]}
+
+
+# sizes at which the two designs are compared: (width, heads, kv heads, head size, ff, vocabulary)
+COMPARISON_SIZES = {"w1024": (1024, 8, 2, 128, 2816, 32000), "w2048": (2048, 16, 4, 128, 5632, 32000)}

@@ -50,6 +50,13 @@ struct AttnParams {
     float* partial;        // split kernel: [rows_total * n_heads][n_chunks][head_dim + 2]
     int n_chunks;
     int chunk_keys;        // split kernel: keys per chunk, a multiple of SPLIT_KEYS
+    // The extended tiles form (EXT): a window that keeps the first tokens visible, a sink per
+    // head in the softmax's denominator, and a sigmoid output gate with a scale.
+    int keep_first;        // with a window: keys below this stay visible to every later row
+    const float* sinks;    // [n_heads], natural-log units, or null
+    const __nv_bfloat16* gate;   // rows of gate logits laid out like `out`, or null
+    int gate_stride;
+    float out_scale;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -219,7 +226,7 @@ struct QFrags {
 // Rows g = lane / 4 and g + 8.  `masked`: some key of the tile may lie outside a
 // row's range (after its position, before its window, or past the end); when
 // the caller knows that none does, the per-element tests are skipped.
-template <int HD_MAX, int NK, bool EXACT>
+template <int HD_MAX, int NK, bool EXACT, bool EXT = false>
 __device__ __forceinline__ void attend_tile(const AttnParams& p, const QFrags<HD_MAX>& q,
                                             const __nv_bfloat16* k_smem,
                                             const __nv_bfloat16* v_smem, int pitch_, bool masked,
@@ -262,8 +269,13 @@ __device__ __forceinline__ void attend_tile(const AttnParams& p, const QFrags<HD
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = key0 + j * 8 + 2 * t + e;
-                if (key > hi_a || key < lo_a) s[j][e] = -INFINITY;
-                if (key > hi_b || key < lo_b) s[j][2 + e] = -INFINITY;
+                if (EXT) {       // keys below keep_first stay visible behind the window
+                    if (key > hi_a || (key < lo_a && key >= p.keep_first)) s[j][e] = -INFINITY;
+                    if (key > hi_b || (key < lo_b && key >= p.keep_first)) s[j][2 + e] = -INFINITY;
+                } else {
+                    if (key > hi_a || key < lo_a) s[j][e] = -INFINITY;
+                    if (key > hi_b || key < lo_b) s[j][2 + e] = -INFINITY;
+                }
             }
         }
     }
@@ -356,7 +368,7 @@ __device__ __forceinline__ void load_q_rows(const AttnParams& p, int row_base, i
 // ---------------------------------------------------------------------------
 // tiles kernel
 // ---------------------------------------------------------------------------
-template <int HD_MAX, bool EXACT>
+template <int HD_MAX, bool EXACT, bool EXT = false>
 __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p) {
     cb_pdl_trigger();
     cb_pdl_wait();
@@ -385,7 +397,11 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     int key_lo = p.window > 0 ? max(0, min_pos - p.window + 1) : 0;
     key_lo = key_lo / TILE_KEYS * TILE_KEYS;
     const int key_end = max_pos + 1;
-    const int n_tiles = (key_end - key_lo + TILE_KEYS - 1) / TILE_KEYS;
+    // EXT: the tiles that hold the kept first tokens come first, if the window has left them
+    const int keep_tiles = (EXT && p.window > 0 && p.keep_first > 0)
+                               ? min((p.keep_first + TILE_KEYS - 1) / TILE_KEYS, key_lo / TILE_KEYS) : 0;
+    const int n_tiles = keep_tiles + (key_end - key_lo + TILE_KEYS - 1) / TILE_KEYS;
+    auto tile_key0 = [&](int i) { return i < keep_tiles ? i * TILE_KEYS : key_lo + (i - keep_tiles) * TILE_KEYS; };
 
     // this warp's two rows
     const int row_a = qt * 64 + warp * 16 + g, row_b = row_a + 8;
@@ -410,13 +426,13 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     const int stage_elems = 2 * TILE_KEYS * pitch;
     KvLoader<HD_MAX, 128, TILE_KEYS> loader;
     loader.init(p, kv_head, pitch, threadIdx.x);
-    loader.load(p, table, key_lo, key_end, kv_smem, kv_smem + TILE_KEYS * pitch);
+    loader.load(p, table, tile_key0(0), key_end, kv_smem, kv_smem + TILE_KEYS * pitch);
     cp_async_commit();
     for (int i = 0; i < n_tiles; ++i) {
         const int st = i & 1;
         if (i + 1 < n_tiles) {
             __nv_bfloat16* nxt = kv_smem + (st ^ 1) * stage_elems;
-            loader.load(p, table, key_lo + (i + 1) * TILE_KEYS, key_end, nxt, nxt + TILE_KEYS * pitch);
+            loader.load(p, table, tile_key0(i + 1), key_end, nxt, nxt + TILE_KEYS * pitch);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -424,12 +440,13 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
         }
         __syncthreads();
         if (i == 0) qf.init(q_smem + warp * 16 * pitch, pitch, p.head_dim);   // the rows are in place now
-        const int key0 = key_lo + i * TILE_KEYS;
+        const int key0 = tile_key0(i);
         if (key0 <= warp_max_pos) {
             const __nv_bfloat16* ks = kv_smem + st * stage_elems;
             // no test per element if every key of the tile is inside every row's range
-            const bool interior = key0 + TILE_KEYS - 1 <= warp_min_pos && key0 >= warp_max_lo;
-            attend_tile<HD_MAX, TILE_KEYS, EXACT>(p, qf, ks, ks + TILE_KEYS * pitch, pitch, !interior,
+            const bool interior = key0 + TILE_KEYS - 1 <= warp_min_pos && key0 >= warp_max_lo &&
+                                  i >= keep_tiles;
+            attend_tile<HD_MAX, TILE_KEYS, EXACT, EXT>(p, qf, ks, ks + TILE_KEYS * pitch, pitch, !interior,
                                                   key0, pos_a, pos_b, lo_a, lo_b, key_end, o, m_a,
                                                   m_b, l_a, l_b);
         }
@@ -439,22 +456,53 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-    const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+    float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+    if (EXT) {
+        // the sink joins the denominator: l += exp(sink - m), with no value; m is in log2 units
+        if (p.sinks != nullptr) {
+            if (row_a < n_rows) {
+                const float sk = p.sinks[kv_head * n_rep + row_a % n_rep] * LOG2E;
+                const float top = fmaxf(m_a, sk);
+                const float corr = exp2f(m_a - top);
+                inv_a = corr / (l_a * corr + exp2f(sk - top));
+            }
+            if (row_b < n_rows) {
+                const float sk = p.sinks[kv_head * n_rep + row_b % n_rep] * LOG2E;
+                const float top = fmaxf(m_b, sk);
+                const float corr = exp2f(m_b - top);
+                inv_b = corr / (l_b * corr + exp2f(sk - top));
+            }
+        }
+        inv_a *= p.out_scale;
+        inv_b *= p.out_scale;
+    }
 #pragma unroll
     for (int n = 0; n < HD_MAX / 8; ++n) {
         if (n * 8 < p.head_dim) {
             const int col = n * 8 + 2 * t;
             if (row_a < n_rows) {
                 const int tok = row_base + row_a / n_rep, head = kv_head * n_rep + row_a % n_rep;
+                float x = o[n][0] * inv_a, y = o[n][1] * inv_a;
+                if (EXT && p.gate != nullptr) {
+                    const __nv_bfloat162 gt = *reinterpret_cast<const __nv_bfloat162*>(
+                        p.gate + (size_t)tok * p.gate_stride + (size_t)head * p.head_dim + col);
+                    x *= 1.0f / (1.0f + __expf(-__bfloat162float(gt.x)));
+                    y *= 1.0f / (1.0f + __expf(-__bfloat162float(gt.y)));
+                }
                 *reinterpret_cast<uint32_t*>(p.out + (size_t)tok * p.out_stride +
-                                             (size_t)head * p.head_dim + col) =
-                    pack_bf16(o[n][0] * inv_a, o[n][1] * inv_a);
+                                             (size_t)head * p.head_dim + col) = pack_bf16(x, y);
             }
             if (row_b < n_rows) {
                 const int tok = row_base + row_b / n_rep, head = kv_head * n_rep + row_b % n_rep;
+                float x = o[n][2] * inv_b, y = o[n][3] * inv_b;
+                if (EXT && p.gate != nullptr) {
+                    const __nv_bfloat162 gt = *reinterpret_cast<const __nv_bfloat162*>(
+                        p.gate + (size_t)tok * p.gate_stride + (size_t)head * p.head_dim + col);
+                    x *= 1.0f / (1.0f + __expf(-__bfloat162float(gt.x)));
+                    y *= 1.0f / (1.0f + __expf(-__bfloat162float(gt.y)));
+                }
                 *reinterpret_cast<uint32_t*>(p.out + (size_t)tok * p.out_stride +
-                                             (size_t)head * p.head_dim + col) =
-                    pack_bf16(o[n][2] * inv_b, o[n][3] * inv_b);
+                                             (size_t)head * p.head_dim + col) = pack_bf16(x, y);
             }
         }
     }
@@ -715,26 +763,26 @@ __global__ void __launch_bounds__(128) attention_split_kernel(const AttnParams p
     }
 }
 
-template <int HD_MAX, bool EXACT>
+template <int HD_MAX, bool EXACT, bool EXT = false>
 int launch_tiles_as(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
     const int pitch = p.head_dim + 8;
     const int smem = (64 + 4 * TILE_KEYS) * pitch * 2;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tiles_kernel<HD_MAX, EXACT>,
+        cudaError_t e = cudaFuncSetAttribute(attention_tiles_kernel<HD_MAX, EXACT, EXT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(max_q_tiles, p.n_kv_heads, n_requests);
-    cb_launch(attention_tiles_kernel<HD_MAX, EXACT>, dim3(grid), dim3(128), smem, s, p);
+    cb_launch(attention_tiles_kernel<HD_MAX, EXACT, EXT>, dim3(grid), dim3(128), smem, s, p);
     return cb_last_error();
 }
 
-template <int HD_MAX>
+template <int HD_MAX, bool EXT = false>
 int launch_tiles(const AttnParams& p, int n_requests, int max_q_tiles, cudaStream_t s) {
-    return p.head_dim == HD_MAX ? launch_tiles_as<HD_MAX, true>(p, n_requests, max_q_tiles, s)
-                                : launch_tiles_as<HD_MAX, false>(p, n_requests, max_q_tiles, s);
+    return p.head_dim == HD_MAX ? launch_tiles_as<HD_MAX, true, EXT>(p, n_requests, max_q_tiles, s)
+                                : launch_tiles_as<HD_MAX, false, EXT>(p, n_requests, max_q_tiles, s);
 }
 
 template <int HD_MAX, bool EXACT>
@@ -818,6 +866,11 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
     p.page_tokens = page_tokens;
     p.scale_log2 = scale * LOG2E;
     p.window = window;
+    p.keep_first = 0;
+    p.sinks = nullptr;
+    p.gate = nullptr;
+    p.gate_stride = 0;
+    p.out_scale = 1.0f;
     p.partial = partial;
     p.n_chunks = n_chunks;
     p.chunk_keys = chunk_keys > 0 ? chunk_keys : SPLIT_KEYS;
@@ -843,4 +896,56 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
     else if (head_dim <= 128) rc = launch_split<128>(p, n_requests, q_tiles, counters, s);
     else rc = launch_split<256>(p, n_requests, q_tiles, counters, s);
     return rc;
+}
+
+// The extended tiles form, for prompts' portions and decoded tokens alike: a row at position p
+// sees j <= p with p - j < window or j < keep_first (window 0: every earlier key); sinks
+// ([n_heads], may be null) join each head's denominator as exp(sink); the result is multiplied
+// by sigmoid(gate) (rows laid out like `out`, may be null) and by out_scale.  q: rows of
+// n_heads * head_dim at q_stride.  Keys and values have the same size.
+CB_EXPORT int cb_attention_mma_sink(const void* q, int q_stride, void* out, int out_stride,
+                                    const void* gate, int gate_stride, const void* k_cache,
+                                    const void* v_cache, const float* sinks, const int* req_row_start,
+                                    const int* req_first_pos, const int* block_table, int table_stride,
+                                    int n_requests, int max_new_tokens, int n_heads, int n_kv_heads,
+                                    int head_dim, int page_tokens, float scale, int window,
+                                    int keep_first, float out_scale, void* stream) {
+    if (n_requests <= 0 || max_new_tokens <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 256 || (head_dim & 15) || n_heads % n_kv_heads != 0 ||
+        (q_stride & 7) || (out_stride & 1) || (gate_stride & 1) || ((uintptr_t)q & 15) ||
+        ((uintptr_t)out & 3) || ((uintptr_t)gate & 3) || ((uintptr_t)k_cache & 15) ||
+        ((uintptr_t)v_cache & 15) || keep_first < 0)
+        return CB_ERR_UNSUPPORTED;
+    AttnParams p;
+    p.qkv = (const __nv_bfloat16*)q;
+    p.qkv_stride = q_stride;
+    p.out = (__nv_bfloat16*)out;
+    p.out_stride = out_stride;
+    p.k_cache = (const __nv_bfloat16*)k_cache;
+    p.v_cache = (const __nv_bfloat16*)v_cache;
+    p.req_row_start = req_row_start;
+    p.req_first_pos = req_first_pos;
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.n_heads = n_heads;
+    p.n_kv_heads = n_kv_heads;
+    p.head_dim = head_dim;
+    p.page_tokens = page_tokens;
+    p.scale_log2 = scale * LOG2E;
+    p.window = window;
+    p.keep_first = window > 0 ? keep_first : 0;
+    p.sinks = sinks;
+    p.gate = (const __nv_bfloat16*)gate;
+    p.gate_stride = gate_stride;
+    p.out_scale = out_scale;
+    p.partial = nullptr;
+    p.n_chunks = 0;
+    p.chunk_keys = SPLIT_KEYS;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int q_tiles = (max_new_tokens * (n_heads / n_kv_heads) + 63) / 64;
+    if (head_dim <= 16) return launch_tiles<16, true>(p, n_requests, q_tiles, s);
+    if (head_dim <= 32) return launch_tiles<32, true>(p, n_requests, q_tiles, s);
+    if (head_dim <= 64) return launch_tiles<64, true>(p, n_requests, q_tiles, s);
+    if (head_dim <= 128) return launch_tiles<128, true>(p, n_requests, q_tiles, s);
+    return launch_tiles<256, true>(p, n_requests, q_tiles, s);
 }

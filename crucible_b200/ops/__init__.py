@@ -61,8 +61,42 @@ _scratch = {}       # per-device scratch of kernels that need some beyond inputs
 LAUNCHES = [0]      # kernels launched through this module (graph replays add their own)
 
 
+# Kernel timing for the benchmark's table (eager steps only): when TIMER[0] is a list,
+# every launch leaves a CUDA event behind it; the time between two events belongs to the
+# launch that left the later one (one stream, nothing else in between).
+TIMER = [None]
+
+
+def _tick(what: str) -> None:
+    marks = TIMER[0]
+    if marks is not None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        marks.append((what, e))
+
+
+def timed_launches(fn):
+    """Runs fn() with the timer on; returns {launch name: (milliseconds, launches)}."""
+    start = torch.cuda.Event(enable_timing=True)
+    TIMER[0] = marks = []
+    try:
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        torch.cuda.synchronize()
+    finally:
+        TIMER[0] = None
+    out, before = {}, start
+    for what, e in marks:
+        ms, n = out.get(what, (0.0, 0))
+        out[what] = (ms + before.elapsed_time(e), n + 1)
+        before = e
+    return out
+
+
 def _check(code: int, what: str) -> None:
     LAUNCHES[0] += 1
+    _tick(what)
     if code != 0:
         lib = build.load("elementwise")
         lib.cb_error_string.restype = ctypes.c_char_p

@@ -49,6 +49,9 @@ def attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
         raise KernelError("sink attention: one float32 sink per query head")
     k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
     table = ctx.block_table(binding.group)
+    if _tensor_cores(q, gate, out, sinks, n_heads, n_kv_heads, key_dim, value_dim, scale, window,
+                     keep_first, out_scale, ctx, cache, k_cache, v_cache, table):
+        return
     lib = build.load("sink_attention")
     _check(lib.cb_sink_attention(
         _ptr(q), _c_int(q.stride(0)), _ptr(gate), _c_int(gate.stride(0) if gate is not None else 0),
@@ -57,3 +60,32 @@ def attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
         _c_int(q.shape[0]), _c_int(n_heads), _c_int(n_kv_heads), _c_int(key_dim), _c_int(value_dim),
         _c_int(cache.page_tokens), _c_float(scale), _c_int(window or 0), _c_int(keep_first),
         _c_float(out_scale), _stream()), "sink attention")
+
+
+TENSOR_CORES = True      # tests switch it off to reach the plain kernel with the same inputs
+
+
+def _tensor_cores(q, gate, out, sinks, n_heads, n_kv_heads, key_dim, value_dim, scale, window,
+                  keep_first, out_scale, ctx, cache, k_cache, v_cache, table) -> bool:
+    """The mma.sync kernel of 64-row tiles (`csrc/attention_mma.cu`, its extended form) for
+    bfloat16 rows whose keys and values have one size, a multiple of 16 up to 256: prompts'
+    portions and decoded tokens in one launch, the rows of a request's query heads that
+    share a key/value head packed into tiles.  Refuses anything else."""
+    host = getattr(ctx, "host", None)
+    if (not TENSOR_CORES or q.dtype != torch.bfloat16 or key_dim != value_dim or key_dim % 16
+            or key_dim > 256 or host is None or q.stride(0) % 8 or out.stride(0) % 2
+            or (gate is not None and gate.stride(0) % 2)):
+        return False
+    from . import tensor_core  # noqa: F401  (registers the module)
+    lib = build.load("attention_mma")
+    code = lib.cb_attention_mma_sink(
+        _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(gate),
+        _c_int(gate.stride(0) if gate is not None else 0), _ptr(k_cache), _ptr(v_cache), _ptr(sinks),
+        _ptr(ctx.req_row_start), _ptr(ctx.req_first_pos), _ptr(table), _c_int(table.shape[1]),
+        _c_int(ctx.n_requests), _c_int(host.max_new_tokens), _c_int(n_heads), _c_int(n_kv_heads),
+        _c_int(key_dim), _c_int(cache.page_tokens), _c_float(scale), _c_int(window or 0),
+        _c_int(keep_first), _c_float(out_scale), _stream())
+    if code == 100001:
+        return False
+    _check(code, "sink attention (tensor cores)")
+    return True

@@ -83,8 +83,9 @@ def _done(code: int, what: str) -> bool:
         return False
     if code != 0:
         raise RuntimeError(f"{what} failed to launch (CUDA error {code})")
-    from . import LAUNCHES
+    from . import LAUNCHES, _tick
     LAUNCHES[0] += 1
+    _tick("few rows: " + what)
     return True
 
 

@@ -83,8 +83,11 @@ def check_status(device) -> None:
 
 
 def _count(n: int) -> None:
-    from . import LAUNCHES
+    from . import LAUNCHES, TIMER, _tick
     LAUNCHES[0] += n
+    if TIMER[0] is not None:
+        import sys
+        _tick("tensor cores: " + sys._getframe(1).f_code.co_name)
 
 
 def _stream():

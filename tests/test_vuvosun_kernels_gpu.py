@@ -137,8 +137,12 @@ def _run_attention(case, row_sets):
     out = torch.zeros(T, H * E, device=DEV, dtype=case.proj.dtype)
     binding = SimpleNamespace(group=0, slot=0, write=True)
     for rows in row_sets:
+        # one request that brings these rows (consecutive positions)
+        assert rows == list(range(rows[0], rows[0] + len(rows)))
         ctx = SimpleNamespace(positions=_i32(rows), row_request=_i32([0] * len(rows)),
-                              block_table=lambda g: case.table)
+                              block_table=lambda g: case.table, req_row_start=_i32([0, len(rows)]),
+                              req_first_pos=_i32([rows[0]]), n_requests=1,
+                              host=SimpleNamespace(max_new_tokens=len(rows)))
         proj = case.proj[rows].contiguous()
         act = torch.empty(len(rows), H * E, device=DEV, dtype=proj.dtype)
         k.rotate_norm_append(proj, case.freq, R, H, G, D, E, 1e-5, ctx, case.cache, binding)
@@ -148,17 +152,24 @@ def _run_attention(case, row_sets):
     return out
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,E,tensor_cores", [(torch.float32, 16, False), (torch.bfloat16, 16, False),
+                                                  (torch.bfloat16, 32, False), (torch.bfloat16, 32, True)])
 @pytest.mark.parametrize("how", ["prompt", "portions", "decode"])
-def test_attention_sees_exactly_its_keys(dtype, how):
-    window, keep, page, T = 10, 3, 8, 90
+@pytest.mark.parametrize("window,keep,T", [(10, 3, 90), (70, 5, 300)])
+def test_attention_sees_exactly_its_keys(dtype, E, tensor_cores, how, window, keep, T, monkeypatch):
+    """E == 32 is the keys' size: the bfloat16 rows may then run on the tensor cores (64-key
+    tiles: the longer case has tiles of kept tokens, tiles that are skipped, and rows whose
+    window starts inside a tile)."""
+    from crucible_b200.ops import sink_attention as k
+    monkeypatch.setattr(k, "TENSOR_CORES", tensor_cores)
+    page = 8
     # the last kept token and the first that is not; both sides of a page border; far back
-    spikes = [2, 3, 7, 8, 40]
-    case = _attention_case(dtype, 4, 2, 32, 16, 16, window, keep, page, T, spikes, seed=1)
+    spikes = [keep - 1, keep, 7, 8, 40] + ([63, 64, 130] if T > 200 else [])
+    case = _attention_case(dtype, 4, 2, 32, E, 16, window, keep, page, T, spikes, seed=1)
     if how == "prompt":
         sets = [list(range(T))]
     elif how == "portions":
-        cuts = [0, 2, 9, 11, 12, 49, 51, 80, T]
+        cuts = [0, 2, 9, 11, 12, 49, 51, 80] + ([150, 151, 290] if T > 200 else []) + [T]
         sets = [list(range(a, b)) for a, b in zip(cuts, cuts[1:])]
     else:
         sets = [list(range(5))] + [[t] for t in range(5, T)]
@@ -172,7 +183,7 @@ def test_attention_sees_exactly_its_keys(dtype, how):
     assert rel(out, ref) < TOL[dtype]
     # the test would see a window that is one off: the plain result itself changes there
     H, G, D, E, R, _, _ = case.dims
-    assert (ref[3 + window] - ref[3 + window - 1]).abs().max() > 0.05
+    assert (ref[keep + window] - ref[keep + window - 1]).abs().max() > 0.05
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
