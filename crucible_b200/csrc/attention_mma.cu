@@ -368,7 +368,10 @@ __device__ __forceinline__ void load_q_rows(const AttnParams& p, int row_base, i
 // ---------------------------------------------------------------------------
 // tiles kernel
 // ---------------------------------------------------------------------------
-template <int HD_MAX, bool EXACT, bool EXT = false>
+// SPLIT (with EXT, requests of at most 64 packed rows): block x takes one of n_chunks equal
+// shares of the row tile's list of key tiles and leaves its running maximum, sum and
+// unnormalised result in p.partial; `attention_merge_kernel` adds the shares.
+template <int HD_MAX, bool EXACT, bool EXT = false, bool SPLIT = false>
 __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p) {
     cb_pdl_trigger();
     cb_pdl_wait();
@@ -382,8 +385,9 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     const int n_new = p.req_row_start[req + 1] - row_base;
     const int n_rows = n_new * n_rep;
     const int q_tiles = (n_rows + 63) >> 6;
-    if ((int)blockIdx.x >= q_tiles) return;
-    const int qt = q_tiles - 1 - (int)blockIdx.x;      // heaviest tiles first
+    if (!SPLIT && (int)blockIdx.x >= q_tiles) return;
+    if (SPLIT && n_rows == 0) return;
+    const int qt = SPLIT ? 0 : q_tiles - 1 - (int)blockIdx.x;      // heaviest tiles first
     const int first_pos = p.req_first_pos[req];
     const int* table = p.block_table + (size_t)req * p.table_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -426,11 +430,20 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     const int stage_elems = 2 * TILE_KEYS * pitch;
     KvLoader<HD_MAX, 128, TILE_KEYS> loader;
     loader.init(p, kv_head, pitch, threadIdx.x);
-    loader.load(p, table, tile_key0(0), key_end, kv_smem, kv_smem + TILE_KEYS * pitch);
+    // SPLIT: this block's share of the tiles
+    const int per_chunk = SPLIT ? (n_tiles + p.n_chunks - 1) / p.n_chunks : n_tiles;
+    const int tile_begin = SPLIT ? min(n_tiles, (int)blockIdx.x * per_chunk) : 0;
+    const int tile_end = SPLIT ? min(n_tiles, tile_begin + per_chunk) : n_tiles;
+    if (tile_begin < tile_end)
+        loader.load(p, table, tile_key0(tile_begin), key_end, kv_smem, kv_smem + TILE_KEYS * pitch);
     cp_async_commit();
-    for (int i = 0; i < n_tiles; ++i) {
-        const int st = i & 1;
-        if (i + 1 < n_tiles) {
+    if (SPLIT && tile_begin >= tile_end) {
+        __syncthreads();
+        qf.init(q_smem + warp * 16 * pitch, pitch, p.head_dim);
+    }
+    for (int i = tile_begin; i < tile_end; ++i) {
+        const int st = (i - tile_begin) & 1;
+        if (i + 1 < tile_end) {
             __nv_bfloat16* nxt = kv_smem + (st ^ 1) * stage_elems;
             loader.load(p, table, tile_key0(i + 1), key_end, nxt, nxt + TILE_KEYS * pitch);
             cp_async_commit();
@@ -439,7 +452,7 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
             cp_async_wait<0>();
         }
         __syncthreads();
-        if (i == 0) qf.init(q_smem + warp * 16 * pitch, pitch, p.head_dim);   // the rows are in place now
+        if (i == tile_begin) qf.init(q_smem + warp * 16 * pitch, pitch, p.head_dim);   // the rows are in place now
         const int key0 = tile_key0(i);
         if (key0 <= warp_max_pos) {
             const __nv_bfloat16* ks = kv_smem + st * stage_elems;
@@ -456,6 +469,33 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    if (SPLIT) {
+        // rows of the partials: [request][kv head][chunk][packed row][head_dim + 2]
+        const int max_rows = p.chunk_keys;          // the launch's largest count of packed rows
+        float* base = p.partial + ((((size_t)req * p.n_kv_heads + kv_head) * p.n_chunks + blockIdx.x) *
+                                   max_rows) * (p.head_dim + 2);
+#pragma unroll
+        for (int n = 0; n < HD_MAX / 8; ++n) {
+            if (n * 8 < p.head_dim) {
+                const int col = n * 8 + 2 * t;
+                if (row_a < n_rows)
+                    *reinterpret_cast<float2*>(base + (size_t)row_a * (p.head_dim + 2) + col) =
+                        make_float2(o[n][0], o[n][1]);
+                if (row_b < n_rows)
+                    *reinterpret_cast<float2*>(base + (size_t)row_b * (p.head_dim + 2) + col) =
+                        make_float2(o[n][2], o[n][3]);
+            }
+        }
+        if (t == 0) {
+            if (row_a < n_rows)
+                *reinterpret_cast<float2*>(base + (size_t)row_a * (p.head_dim + 2) + p.head_dim) =
+                    make_float2(m_a, l_a);
+            if (row_b < n_rows)
+                *reinterpret_cast<float2*>(base + (size_t)row_b * (p.head_dim + 2) + p.head_dim) =
+                    make_float2(m_b, l_b);
+        }
+        return;
+    }
     float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
     if (EXT) {
         // the sink joins the denominator: l += exp(sink - m), with no value; m is in log2 units
@@ -785,6 +825,83 @@ int launch_tiles(const AttnParams& p, int n_requests, int max_q_tiles, cudaStrea
                                 : launch_tiles_as<HD_MAX, false, EXT>(p, n_requests, max_q_tiles, s);
 }
 
+// Adds the shares that the SPLIT tiles kernel left: one warp per packed row.  The sink joins
+// the denominator here, then the gate and the scale.
+__global__ void __launch_bounds__(128) attention_merge_kernel(const AttnParams p, int max_rows) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int req = blockIdx.z, kv_head = blockIdx.y;
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int n_rep = p.n_heads / p.n_kv_heads;
+    const int row_base = p.req_row_start[req];
+    const int n_rows = (p.req_row_start[req + 1] - row_base) * n_rep;
+    if (row >= n_rows) return;
+    const int hd = p.head_dim, stride = hd + 2;
+    const float* base = p.partial + (((size_t)req * p.n_kv_heads + kv_head) * p.n_chunks * max_rows + row) * stride;
+    const size_t chunk_stride = (size_t)max_rows * stride;
+    float top = -INFINITY;
+    for (int c = 0; c < p.n_chunks; ++c) top = fmaxf(top, base[c * chunk_stride + hd]);
+    const int head = kv_head * n_rep + row % n_rep;
+    float sk = -INFINITY;
+    if (p.sinks != nullptr) {
+        sk = p.sinks[head] * LOG2E;
+        top = fmaxf(top, sk);
+    }
+    float l = p.sinks != nullptr ? exp2f(sk - top) : 0.f;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int c = 0; c < p.n_chunks; ++c) {
+        const float* part = base + c * chunk_stride;
+        const float m = part[hd];
+        if (m == -INFINITY) continue;
+        const float w = exp2f(m - top);
+        l += part[hd + 1] * w;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int f = lane + 32 * i;
+            if (f < hd) acc[i] = fmaf(part[f], w, acc[i]);
+        }
+    }
+    const float inv = l > 0.f ? p.out_scale / l : 0.f;
+    const int tok = row_base + row / n_rep;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int f = lane + 32 * i;
+        if (f < hd) {
+            float x = acc[i] * inv;
+            if (p.gate != nullptr)
+                x *= 1.0f / (1.0f + __expf(-__bfloat162float(
+                                       p.gate[(size_t)tok * p.gate_stride + (size_t)head * hd + f])));
+            p.out[(size_t)tok * p.out_stride + (size_t)head * hd + f] = __float2bfloat16_rn(x);
+        }
+    }
+}
+
+template <int HD_MAX, bool EXACT>
+int launch_tiles_split_as(const AttnParams& p, int n_requests, int max_rows, cudaStream_t s) {
+    const int pitch = p.head_dim + 8;
+    const int smem = (64 + 4 * TILE_KEYS) * pitch * 2;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tiles_kernel<HD_MAX, EXACT, true, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cb_launch(attention_tiles_kernel<HD_MAX, EXACT, true, true>, dim3(p.n_chunks, p.n_kv_heads, n_requests),
+              dim3(128), smem, s, p);
+    cb_launch(attention_merge_kernel, dim3((max_rows + 3) / 4, p.n_kv_heads, n_requests), dim3(128), 0, s,
+              p, max_rows);
+    return cb_last_error();
+}
+
+template <int HD_MAX>
+int launch_tiles_split(const AttnParams& p, int n_requests, int max_rows, cudaStream_t s) {
+    return p.head_dim == HD_MAX ? launch_tiles_split_as<HD_MAX, true>(p, n_requests, max_rows, s)
+                                : launch_tiles_split_as<HD_MAX, false>(p, n_requests, max_rows, s);
+}
+
 template <int HD_MAX, bool EXACT>
 int launch_split_as(const AttnParams& p, int n_requests, int max_q_tiles, int* counters,
                     cudaStream_t s) {
@@ -902,14 +1019,16 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
 // sees j <= p with p - j < window or j < keep_first (window 0: every earlier key); sinks
 // ([n_heads], may be null) join each head's denominator as exp(sink); the result is multiplied
 // by sigmoid(gate) (rows laid out like `out`, may be null) and by out_scale.  q: rows of
-// n_heads * head_dim at q_stride.  Keys and values have the same size.
+// n_heads * head_dim at q_stride.  Keys and values have the same size.  n_chunks > 1 (requests
+// of at most 64 packed rows): the key tiles in that many shares over blocks, and a merge.
 CB_EXPORT int cb_attention_mma_sink(const void* q, int q_stride, void* out, int out_stride,
                                     const void* gate, int gate_stride, const void* k_cache,
                                     const void* v_cache, const float* sinks, const int* req_row_start,
                                     const int* req_first_pos, const int* block_table, int table_stride,
                                     int n_requests, int max_new_tokens, int n_heads, int n_kv_heads,
                                     int head_dim, int page_tokens, float scale, int window,
-                                    int keep_first, float out_scale, void* stream) {
+                                    int keep_first, float out_scale, float* partial, int n_chunks,
+                                    void* stream) {
     if (n_requests <= 0 || max_new_tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim > 256 || (head_dim & 15) || n_heads % n_kv_heads != 0 ||
         (q_stride & 7) || (out_stride & 1) || (gate_stride & 1) || ((uintptr_t)q & 15) ||
@@ -938,11 +1057,24 @@ CB_EXPORT int cb_attention_mma_sink(const void* q, int q_stride, void* out, int 
     p.gate = (const __nv_bfloat16*)gate;
     p.gate_stride = gate_stride;
     p.out_scale = out_scale;
-    p.partial = nullptr;
-    p.n_chunks = 0;
+    p.partial = partial;
+    p.n_chunks = n_chunks;
     p.chunk_keys = SPLIT_KEYS;
     cudaStream_t s = (cudaStream_t)stream;
-    const int q_tiles = (max_new_tokens * (n_heads / n_kv_heads) + 63) / 64;
+    const int max_rows = max_new_tokens * (n_heads / n_kv_heads);
+    if (n_chunks > 1) {
+        // the key tiles of every request's (single) row tile in n_chunks shares, then a merge;
+        // partial: n_requests * n_kv_heads * n_chunks * max_rows * (head_dim + 2) floats
+        if (partial == nullptr || max_rows > 64) return CB_ERR_UNSUPPORTED;
+        p.chunk_keys = max_rows;
+        if (head_dim <= 16) return launch_tiles_split<16>(p, n_requests, max_rows, s);
+        if (head_dim <= 32) return launch_tiles_split<32>(p, n_requests, max_rows, s);
+        if (head_dim <= 64) return launch_tiles_split<64>(p, n_requests, max_rows, s);
+        if (head_dim <= 128) return launch_tiles_split<128>(p, n_requests, max_rows, s);
+        return launch_tiles_split<256>(p, n_requests, max_rows, s);
+    }
+    p.n_chunks = 0;
+    const int q_tiles = (max_rows + 63) / 64;
     if (head_dim <= 16) return launch_tiles<16, true>(p, n_requests, q_tiles, s);
     if (head_dim <= 32) return launch_tiles<32, true>(p, n_requests, q_tiles, s);
     if (head_dim <= 64) return launch_tiles<64, true>(p, n_requests, q_tiles, s);

@@ -13,6 +13,7 @@
 //             normalised rows never go to global memory;
 //   epilogues ACCUM_F32    out[m, n] += dot               (output projections)
 //             STORE_F32    out[m, n]  = dot               (logits)
+//             STORE_BF16   out[m, n]  = bf16(dot)         (joint input projections)
 //             SWIGLU_BF16  out[m, i]  = silu(g_i) * u_i   (gate and up rows paired)
 //             ROPE_APPEND  rows (j, j + hd/2) of a head paired: q rotated and
 //                          stored, k rotated into the request's cache page,
@@ -41,7 +42,7 @@
 
 namespace {
 
-enum SmallEpilogue { ACCUM_F32 = 0, STORE_F32 = 1, SWIGLU_BF16 = 2, ROPE_APPEND = 3 };
+enum SmallEpilogue { ACCUM_F32 = 0, STORE_F32 = 1, SWIGLU_BF16 = 2, ROPE_APPEND = 3, STORE_BF16 = 4 };
 
 struct SmallParams {
     const float* x;               // NORM_IN: fp32 [M, K]
@@ -366,7 +367,11 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
             const int m = nt * 8 + 2 * t + e;
             if (m >= p.M) continue;
             const float df = d[e], ds = d[2 + e];
-            if (EPI == ACCUM_F32 || EPI == STORE_F32) {
+            if (EPI == STORE_BF16) {
+                __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)m * p.ldc;
+                if (ok_f) out[rf] = __float2bfloat16_rn(df);
+                if (ok_s) out[rs] = __float2bfloat16_rn(ds);
+            } else if (EPI == ACCUM_F32 || EPI == STORE_F32) {
                 float* out = (float*)p.out + (size_t)m * p.ldc;
                 if (ok_f) out[rf] = EPI == ACCUM_F32 ? old[nt][e] + df : df;
                 if (ok_s) out[rs] = EPI == ACCUM_F32 ? old[nt][2 + e] + ds : ds;
@@ -458,6 +463,20 @@ CB_EXPORT int cb_small_linear(const float* x, const float* gain, float eps, cons
     cudaStream_t s = (cudaStream_t)stream;
     if (x) return accumulate ? launch_rows<true, ACCUM_F32>(p, s) : launch_rows<true, STORE_F32>(p, s);
     return accumulate ? launch_rows<false, ACCUM_F32>(p, s) : launch_rows<false, STORE_F32>(p, s);
+}
+
+// out[M, N] (bf16) = act W^T.
+CB_EXPORT int cb_small_linear_bf16(const float* x, const float* gain, float eps, const void* a, int lda,
+                                   const void* w, int ldw, void* out, int ldc, int M, int N, int K,
+                                   void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (!sizes_ok(x, gain, a, lda, M, K, ldw, w)) return CB_ERR_UNSUPPORTED;
+    SmallParams p = {};
+    p.x = x; p.gain = gain; p.eps = eps; p.a = (const __nv_bfloat16*)a; p.lda = lda;
+    p.w = (const __nv_bfloat16*)w; p.ldw = ldw; p.M = M; p.K = K; p.N = N;
+    p.n_tiles = (N + 15) / 16; p.out = out; p.ldc = ldc;
+    cudaStream_t s = (cudaStream_t)stream;
+    return x ? launch_rows<true, STORE_BF16>(p, s) : launch_rows<false, STORE_BF16>(p, s);
 }
 
 // out[M, inter] (bf16) = silu(act Wg^T) * (act Wu^T), W = [Wg; Wu] ([2 inter, K]).

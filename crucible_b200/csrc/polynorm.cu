@@ -43,7 +43,7 @@ __global__ void polynorm_kernel(const T* __restrict__ z, int z_stride, const flo
 CB_EXPORT int cb_polynorm(const void* z, int z_stride, const float* coef, void* out, int out_stride,
                           int dtype, int n_rows, int ff, float eps, void* stream) {
     if (n_rows <= 0) return 0;
-    const dim3 grid(n_rows), block(ff <= 2048 ? 128 : 256);
+    const dim3 grid(n_rows), block(ff <= 256 ? 64 : (ff >= 4096 ? 1024 : (ff / 4 + 31) / 32 * 32));
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
         cb_launch(polynorm_kernel<float>, grid, block, 0, s, (const float*)z, z_stride, coef,

@@ -15,10 +15,11 @@
 // update of the convolution's state, the recurrence itself, and the per-head RMS
 // norm with gain and output gate.  Everything after the projections is fp32.
 //
-// The recurrence walks a request's tokens in order.  A block owns 32 columns of one
-// head's S; four lanes share a column, each with a quarter of its D entries in
-// registers, so a token costs two passes of D/4 multiply-adds and two shuffles.
-// The tokens' q, k, v and gates are staged in shared memory 16 tokens at a time.
+// The recurrence walks a request's tokens in order.  A block owns 16 columns of one
+// head's S; eight lanes share a column, each with an eighth of its D entries in
+// registers, so a token costs two passes of D/8 multiply-adds and three shuffles each.
+// The tokens' q, k, v and gates are staged in shared memory 16 tokens at a time, by
+// asynchronous copies one chunk ahead.
 #define CB_PDL_BIT 11      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 
@@ -26,13 +27,23 @@ namespace {
 
 constexpr int RULE_DELTA = 0, RULE_MLSTM = 1;
 constexpr int GATE_SILU = 0, GATE_SIGMOID = 1;
-constexpr int COLS = 32;          // columns of S per block
+constexpr int LANES = 8;          // lanes that share a column of S
+constexpr int COLS = 128 / LANES; // columns of S per block
 constexpr int CHUNK = 16;         // tokens staged at a time
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ float logsigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+template <int BYTES>
+__device__ __forceinline__ void cp_async(float* smem, const float* gmem) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+    if (BYTES == 16)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem) : "memory");
+    else
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem) : "memory");
+}
 
 __device__ __forceinline__ float* state_at(unsigned char* state, long slot_stride, int slot, long off) {
     return reinterpret_cast<float*>(state + (size_t)slot * slot_stride + off);
@@ -147,6 +158,9 @@ __global__ void mlstm_prepare_kernel(const T* __restrict__ proj, int proj_stride
 // qkv: fp32 [rows][C] with q heads at q_off, k heads at k_off (both n_qk_heads of D), v heads at
 // v_off (n_heads of E).  sc0, sc1: fp32 [rows][H]: (decay, beta) or (log keep, log in).
 // State: S at s_off [H][D][E]; mLSTM: n at n_off [H][D], m at m_off [H].
+// A block: COLS columns x LANES lanes; lane `part` of a column owns entries part * P .. part * P + P - 1
+// of it.  The staged k and q rows are padded by four floats per part, so that the parts'
+// 16-byte reads fall on different banks.
 template <int P, int RULE>
 __global__ void __launch_bounds__(128) matrix_memory_kernel(
     const float* __restrict__ qkv, int C, int q_off, int k_off, int v_off,
@@ -156,52 +170,97 @@ __global__ void __launch_bounds__(128) matrix_memory_kernel(
     float* __restrict__ out, int n_heads, int n_qk_heads, int D, int E) {
     cb_pdl_trigger();
     cb_pdl_wait();
-    extern __shared__ float stage[];
-    float* sk = stage;                       // [CHUNK][D]
-    float* sq = sk + CHUNK * D;              // [CHUNK][D]
-    float* sv = sq + CHUNK * D;              // [CHUNK][COLS]
-    float* s0 = sv + CHUNK * COLS;           // [CHUNK]
-    float* s1 = s0 + CHUNK;                  // [CHUNK]
+    constexpr int PITCH = LANES * (P + 4);
+    constexpr int BUF = CHUNK * (2 * PITCH + COLS) + 2 * CHUNK;      // floats of one stage
+    extern __shared__ __align__(16) float stage[];
     const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * COLS;
     const int g = head / (n_heads / n_qk_heads);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int col = col0 + warp * 8 + (lane >> 2), part = lane & 3;
+    const int col = col0 + warp * (32 / LANES) + lane / LANES, part = lane % LANES;
     const bool live = col < E;
     const int row0 = req_row_start[r], row1 = req_row_start[r + 1];
     const int slot = req_state_slot[r];
     float* S = state_at(state, slot_stride, slot, s_off) + (size_t)head * D * E;
     float* N = RULE == RULE_MLSTM ? state_at(state, slot_stride, slot, n_off) + (size_t)head * D : nullptr;
     float* M = RULE == RULE_MLSTM ? state_at(state, slot_stride, slot, m_off) + head : nullptr;
+    // the padding of the staged rows and the columns beyond E stay zero
+    for (int i = threadIdx.x; i < 2 * BUF; i += blockDim.x) stage[i] = 0.f;
     float s[P], n[P];
     float m = 0.f;
 #pragma unroll
     for (int i = 0; i < P; ++i) {
-        const int d = part + 4 * i;
+        const int d = part * P + i;
         s[i] = (live && d < D) ? S[(size_t)d * E + col] : 0.f;
         n[i] = (RULE == RULE_MLSTM && d < D) ? N[d] : 0.f;
     }
     if (RULE == RULE_MLSTM) m = *M;
-    for (int base = row0; base < row1; base += CHUNK) {
+    __syncthreads();
+    // 16-byte copies if every row of q and k starts on a 16-byte boundary
+    const bool vec = ((C | q_off | k_off | D) & 3) == 0;
+    // a chunk's q, k, v and gates on their way into one of the two stages (asynchronous
+    // copies: the next chunk travels while this one is worked on)
+    auto fetch = [&](int base, int buf) {
+        float* sk = stage + buf * BUF;
+        float* sq = sk + CHUNK * PITCH;
+        float* sv = sq + CHUNK * PITCH;
+        float* s0 = sv + CHUNK * COLS;
+        float* s1 = s0 + CHUNK;
         const int cnt = min(CHUNK, row1 - base);
-        __syncthreads();
-        for (int i = threadIdx.x; i < cnt * D; i += blockDim.x) {
-            const int tt = i / D, d = i - tt * D;
-            const float* src = qkv + (size_t)(base + tt) * C + (size_t)g * D + d;
-            sk[tt * D + d] = src[k_off];
-            sq[tt * D + d] = src[q_off];
+        if (vec) {
+            const int per_row = D >> 2;
+            for (int i = threadIdx.x; i < cnt * per_row; i += blockDim.x) {
+                const int tt = i / per_row, d = (i - tt * per_row) << 2;
+                const float* src = qkv + (size_t)(base + tt) * C + (size_t)g * D + d;
+                const int at = tt * PITCH + d + (d / P) * 4;
+                cp_async<16>(sk + at, src + k_off);
+                cp_async<16>(sq + at, src + q_off);
+            }
+        } else {
+            for (int i = threadIdx.x; i < cnt * D; i += blockDim.x) {
+                const int tt = i / D, d = i - tt * D;
+                const float* src = qkv + (size_t)(base + tt) * C + (size_t)g * D + d;
+                const int at = tt * PITCH + d + (d / P) * 4;
+                cp_async<4>(sk + at, src + k_off);
+                cp_async<4>(sq + at, src + q_off);
+            }
         }
         for (int i = threadIdx.x; i < cnt * COLS; i += blockDim.x) {
             const int tt = i / COLS, c = i - tt * COLS;
-            sv[i] = col0 + c < E ? qkv[(size_t)(base + tt) * C + v_off + (size_t)head * E + col0 + c] : 0.f;
+            if (col0 + c < E)
+                cp_async<4>(sv + i, qkv + (size_t)(base + tt) * C + v_off + (size_t)head * E + col0 + c);
         }
         if (threadIdx.x < cnt) {
-            s0[threadIdx.x] = sc0[(size_t)(base + threadIdx.x) * n_heads + head];
-            s1[threadIdx.x] = sc1[(size_t)(base + threadIdx.x) * n_heads + head];
+            cp_async<4>(s0 + threadIdx.x, sc0 + (size_t)(base + threadIdx.x) * n_heads + head);
+            cp_async<4>(s1 + threadIdx.x, sc1 + (size_t)(base + threadIdx.x) * n_heads + head);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (row0 < row1) fetch(row0, 0);
+    int buf = 0;
+    for (int base = row0; base < row1; base += CHUNK, buf ^= 1) {
+        const int cnt = min(CHUNK, row1 - base);
+        if (base + CHUNK < row1) {
+            fetch(base + CHUNK, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        const float* sk = stage + buf * BUF;
+        const float* sq = sk + CHUNK * PITCH;
+        const float* sv = sq + CHUNK * PITCH;
+        const float* s0 = sv + CHUNK * COLS;
+        const float* s1 = s0 + CHUNK;
         for (int tt = 0; tt < cnt; ++tt) {
-            const float* kk = sk + tt * D;
-            const float* qq = sq + tt * D;
+            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * PITCH + part * (P + 4));
+            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * PITCH + part * (P + 4));
+            float kk[P], qq[P];
+#pragma unroll
+            for (int j = 0; j < P / 4; ++j) {
+                const float4 a = k4[j], b = q4[j];
+                kk[4 * j] = a.x; kk[4 * j + 1] = a.y; kk[4 * j + 2] = a.z; kk[4 * j + 3] = a.w;
+                qq[4 * j] = b.x; qq[4 * j + 1] = b.y; qq[4 * j + 2] = b.z; qq[4 * j + 3] = b.w;
+            }
             const float v = sv[tt * COLS + (col - col0)];
             float o;
             if (RULE == RULE_DELTA) {
@@ -209,26 +268,22 @@ __global__ void __launch_bounds__(128) matrix_memory_kernel(
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int i = 0; i < P; ++i) {
-                    const int d = part + 4 * i;
                     s[i] *= decay;
-                    if (d < D) acc[i & 3] = fmaf(s[i], kk[d], acc[i & 3]);
+                    acc[i & 3] = fmaf(s[i], kk[i], acc[i & 3]);
                 }
                 float rk = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-                rk += __shfl_xor_sync(0xffffffffu, rk, 1);
-                rk += __shfl_xor_sync(0xffffffffu, rk, 2);
+#pragma unroll
+                for (int w = 1; w < LANES; w <<= 1) rk += __shfl_xor_sync(0xffffffffu, rk, w);
                 const float u = beta * (v - rk);
                 float oc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int i = 0; i < P; ++i) {
-                    const int d = part + 4 * i;
-                    if (d < D) {
-                        s[i] = fmaf(kk[d], u, s[i]);
-                        oc[i & 3] = fmaf(s[i], qq[d], oc[i & 3]);
-                    }
+                    s[i] = fmaf(kk[i], u, s[i]);
+                    oc[i & 3] = fmaf(s[i], qq[i], oc[i & 3]);
                 }
                 o = (oc[0] + oc[1]) + (oc[2] + oc[3]);
-                o += __shfl_xor_sync(0xffffffffu, o, 1);
-                o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+                for (int w = 1; w < LANES; w <<= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
             } else {
                 const float f = s0[tt], in = s1[tt];
                 const float m_new = fmaxf(f + m, in);
@@ -238,29 +293,27 @@ __global__ void __launch_bounds__(128) matrix_memory_kernel(
                 float oc[4] = {0.f, 0.f, 0.f, 0.f}, nc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int i = 0; i < P; ++i) {
-                    const int d = part + 4 * i;
-                    if (d < D) {
-                        const float kd = kk[d], qd = qq[d];
-                        s[i] = fmaf(kd, bv, a * s[i]);
-                        n[i] = fmaf(b, kd, a * n[i]);
-                        oc[i & 3] = fmaf(s[i], qd, oc[i & 3]);
-                        nc[i & 3] = fmaf(n[i], qd, nc[i & 3]);
-                    }
+                    s[i] = fmaf(kk[i], bv, a * s[i]);
+                    n[i] = fmaf(b, kk[i], a * n[i]);
+                    oc[i & 3] = fmaf(s[i], qq[i], oc[i & 3]);
+                    nc[i & 3] = fmaf(n[i], qq[i], nc[i & 3]);
                 }
                 o = (oc[0] + oc[1]) + (oc[2] + oc[3]);
                 float nq = (nc[0] + nc[1]) + (nc[2] + nc[3]);
-                o += __shfl_xor_sync(0xffffffffu, o, 1);
-                nq += __shfl_xor_sync(0xffffffffu, nq, 1);
-                o += __shfl_xor_sync(0xffffffffu, o, 2);
-                nq += __shfl_xor_sync(0xffffffffu, nq, 2);
+#pragma unroll
+                for (int w = 1; w < LANES; w <<= 1) {
+                    o += __shfl_xor_sync(0xffffffffu, o, w);
+                    nq += __shfl_xor_sync(0xffffffffu, nq, w);
+                }
                 o = o / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
             }
             if (live && part == 0) out[(size_t)(base + tt) * n_heads * E + (size_t)head * E + col] = o;
         }
+        __syncthreads();          // the stage is free for the chunk after next
     }
 #pragma unroll
     for (int i = 0; i < P; ++i) {
-        const int d = part + 4 * i;
+        const int d = part * P + i;
         if (live && d < D) S[(size_t)d * E + col] = s[i];
         if (RULE == RULE_MLSTM && blockIdx.z == 0 && col == 0 && d < D) N[d] = n[i];
     }
@@ -301,15 +354,27 @@ int launch_memory(const float* qkv, int C, int q_off, int k_off, int v_off, cons
                   unsigned char* state, long slot_stride, long s_off, long n_off, long m_off, float* out,
                   int n_requests, int n_heads, int n_qk_heads, int D, int E, cudaStream_t s) {
     const dim3 grid(n_requests, n_heads, (E + COLS - 1) / COLS), block(128);
-    const size_t smem = (size_t)(CHUNK * (2 * D + COLS) + 2 * CHUNK) * sizeof(float);
+    const int P = D <= 32 ? 4 : (D <= 64 ? 8 : (D <= 128 ? 16 : 32));
+    const size_t smem = 2 * (size_t)(CHUNK * (2 * LANES * (P + 4) + COLS) + 2 * CHUNK) * sizeof(float);
 #define CB_MEM(PP)                                                                                 \
+    {                                                                                              \
+    if (smem > 48 * 1024) {                                                                        \
+        static bool configured = false;                                                            \
+        if (!configured) {                                                                         \
+            cudaError_t e = cudaFuncSetAttribute(matrix_memory_kernel<PP, RULE>,                   \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+            if (e != cudaSuccess) return (int)e;                                                   \
+            configured = true;                                                                     \
+        }                                                                                          \
+    }                                                                                              \
     cb_launch(matrix_memory_kernel<PP, RULE>, grid, block, smem, s, qkv, C, q_off, k_off, v_off, sc0, \
               sc1, req_row_start, req_state_slot, state, slot_stride, s_off, n_off, m_off, out,     \
-              n_heads, n_qk_heads, D, E)
-    if (D <= 32) CB_MEM(8);
-    else if (D <= 64) CB_MEM(16);
-    else if (D <= 128) CB_MEM(32);
-    else if (D <= 256) CB_MEM(64);
+              n_heads, n_qk_heads, D, E);                                                          \
+    }
+    if (D <= 32) CB_MEM(4)
+    else if (D <= 64) CB_MEM(8)
+    else if (D <= 128) CB_MEM(16)
+    else if (D <= 256) CB_MEM(32)
     else return CB_ERR_UNSUPPORTED;
 #undef CB_MEM
     return cb_last_error();
@@ -327,7 +392,7 @@ CB_EXPORT int cb_delta_prepare(const void* proj, int proj_stride, int dtype, con
     if (n_rows <= 0) return 0;
     const int C = 2 * n_kv_heads * key_dim + n_heads * value_dim;
     if (taps < 1 || C > 12000 || n_heads % n_kv_heads != 0) return CB_ERR_UNSUPPORTED;
-    const dim3 grid(n_rows), block(C <= 1024 ? 128 : 256);
+    const dim3 grid(n_rows), block(C <= 256 ? 128 : (C >= 2048 ? 1024 : (C / 2 + 31) / 32 * 32));
     const size_t smem = (size_t)C * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
@@ -364,7 +429,8 @@ CB_EXPORT int cb_mlstm_prepare(const void* proj, int proj_stride, int dtype, con
                                float* log_keep, float* log_in, int n_rows, int n_heads, int key_dim,
                                int value_dim, void* stream) {
     if (n_rows <= 0) return 0;
-    const dim3 grid(n_rows), block(256);
+    const int C = n_heads * (2 * key_dim + value_dim);
+    const dim3 grid(n_rows), block(C <= 512 ? 128 : (C >= 4096 ? 1024 : (C / 4 + 31) / 32 * 32));
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
         cb_launch(mlstm_prepare_kernel<float>, grid, block, 0, s, (const float*)proj, proj_stride,

@@ -16,7 +16,11 @@ namespace {
 
 constexpr int MAX_STREAMS = 8;
 
-__host__ __device__ inline int threads_for(int width) { return width <= 1024 ? 128 : 256; }
+// half a thread per feature, so a decode step's few rows still have many loads in flight
+__host__ __device__ inline int threads_for(int width) {
+    const int t = ((width + 1) / 2 + 31) / 32 * 32;
+    return t < 64 ? 64 : (t > 512 ? 512 : t);      // 512: the write kernel holds every stream of a feature in registers
+}
 
 // x0 = rmsnorm(table[id]) * gain, written to all S streams of the token
 template <typename T>

@@ -78,13 +78,26 @@ def _tensor_cores(q, gate, out, sinks, n_heads, n_kv_heads, key_dim, value_dim, 
         return False
     from . import tensor_core  # noqa: F401  (registers the module)
     lib = build.load("attention_mma")
+    # Few rows per request (decoded tokens, short portions): one row tile each, so the blocks
+    # are few; the key tiles are then dealt to several blocks and merged.  The number of shares
+    # is a function of the step's shape; any number gives the same sums up to rounding.
+    max_rows = host.max_new_tokens * (n_heads // n_kv_heads)
+    n_chunks, partial = 1, None
+    if max_rows <= 64:
+        reach = host.context_bucket if window is None else min(window + 64, host.context_bucket)
+        tiles = -(-reach // 64) + (-(-keep_first // 64) if window is not None else 0)
+        n_chunks = max(1, min(tiles // 2, 296 // max(1, n_kv_heads * ctx.n_requests)))
+        if n_chunks > 1:
+            partial = ctx.scratch("sink_attention.partial",
+                                  (ctx.n_requests * n_kv_heads * n_chunks * max_rows * (key_dim + 2),),
+                                  torch.float32)
     code = lib.cb_attention_mma_sink(
         _ptr(q), _c_int(q.stride(0)), _ptr(out), _c_int(out.stride(0)), _ptr(gate),
         _c_int(gate.stride(0) if gate is not None else 0), _ptr(k_cache), _ptr(v_cache), _ptr(sinks),
         _ptr(ctx.req_row_start), _ptr(ctx.req_first_pos), _ptr(table), _c_int(table.shape[1]),
         _c_int(ctx.n_requests), _c_int(host.max_new_tokens), _c_int(n_heads), _c_int(n_kv_heads),
         _c_int(key_dim), _c_int(cache.page_tokens), _c_float(scale), _c_int(window or 0),
-        _c_int(keep_first), _c_float(out_scale), _stream())
+        _c_int(keep_first), _c_float(out_scale), _ptr(partial), _c_int(n_chunks), _stream())
     if code == 100001:
         return False
     _check(code, "sink attention (tensor cores)")

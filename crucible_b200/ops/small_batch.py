@@ -114,14 +114,21 @@ MAX_OUT_ROWS = 8192     # wider products (the LM head) stream better through the
 
 
 def linear(h: Rows, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -> bool:
-    if (not _weights_ok(w, h.shape[0]) or out.dtype != torch.float32 or out.stride(1) != 1
-            or w.shape[0] > MAX_OUT_ROWS):
+    if (not _weights_ok(w, h.shape[0]) or out.stride(1) != 1 or w.shape[0] > MAX_OUT_ROWS
+            or out.dtype not in (torch.float32, torch.bfloat16)
+            or (accumulate and out.dtype != torch.float32)):
         return False
     inp = _input(h, w)
     if inp is None:
         return False
     x, gain, eps, a, lda = inp
     lib = build.load("decode_small")
+    if out.dtype == torch.bfloat16:
+        return _done(lib.cb_small_linear_bf16(_ptr(x), _ptr(gain), _c_float(eps), _ptr(a), _c_int(lda),
+                                              _ptr(w), _c_int(w.stride(0)), _ptr(out),
+                                              _c_int(out.stride(0)), _c_int(h.shape[0]),
+                                              _c_int(w.shape[0]), _c_int(w.shape[1]), _stream()),
+                     "small linear (bf16 result)")
     return _done(lib.cb_small_linear(_ptr(x), _ptr(gain), _c_float(eps), _ptr(a), _c_int(lda),
                                      _ptr(w), _c_int(w.stride(0)), _ptr(out), _c_int(out.stride(0)),
                                      _c_int(h.shape[0]), _c_int(w.shape[0]), _c_int(w.shape[1]),

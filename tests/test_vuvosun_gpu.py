@@ -147,6 +147,27 @@ def test_long_decoding_past_window_and_pages(tmp_path):
         _compare("vu-a", dtype, got, ref)
 
 
+def test_decoding_with_a_long_window_deals_the_keys_to_several_blocks(tmp_path):
+    """A window of 150 keys and two kept tokens: decoded tokens' key tiles are split over
+    blocks and merged (bfloat16, keys and values of one size)."""
+    import copy
+    config = copy.deepcopy(cases.CASES["vu-c"]["config"])
+    for layer in config["layers"]:
+        layer["mixer"]["left"]["mask"] = {"size": 150, "keep_first": 2}
+    model_dir = cases.make_folder(tmp_path, "vu-long", config=config, seed=6)
+    requests = {"r0": helpers.random_tokens(400, 330, 3), "r1": helpers.random_tokens(400, 200, 4)}
+    ref = _reference(model_dir, requests)
+    for dtype in ("bfloat16", "float32"):
+        trace = Trace()
+        trace.step([("r0", requests["r0"][:250], [249]), ("r1", requests["r1"][:120], [119])])
+        for i in range(80):
+            trace.step([("r0", [requests["r0"][250 + i]], [0]), ("r1", [requests["r1"][120 + i]], [0])],
+                       end=["r0", "r1"] if i == 79 else [])
+        engine = helpers.replay_in_process(model_dir, dtype, trace, str(tmp_path / dtype), 640, 8)
+        got = helpers.collect(trace, str(tmp_path / dtype), 400)
+        _compare("vu-long", dtype, got, ref)
+
+
 def test_window_pages_go_back_and_kept_first_pages_stay(tmp_path):
     from crucible_b200.engine.engine import Engine, EngineOptions, StepEntry
     model_dir = cases.make_folder(tmp_path, "vu-a")

@@ -142,7 +142,9 @@ def _run_attention(case, row_sets):
         ctx = SimpleNamespace(positions=_i32(rows), row_request=_i32([0] * len(rows)),
                               block_table=lambda g: case.table, req_row_start=_i32([0, len(rows)]),
                               req_first_pos=_i32([rows[0]]), n_requests=1,
-                              host=SimpleNamespace(max_new_tokens=len(rows)))
+                              host=SimpleNamespace(max_new_tokens=len(rows),
+                                                   context_bucket=256 * (-(-(rows[-1] + 1) // 256))),
+                              scratch=lambda name, shape, dtype: torch.empty(shape, device=DEV, dtype=dtype))
         proj = case.proj[rows].contiguous()
         act = torch.empty(len(rows), H * E, device=DEV, dtype=proj.dtype)
         k.rotate_norm_append(proj, case.freq, R, H, G, D, E, 1e-5, ctx, case.cache, binding)
