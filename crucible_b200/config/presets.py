@@ -65,3 +65,6 @@ def vuvosun(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab
 
 # sizes at which the two designs are compared: (width, heads, kv heads, head size, ff, vocabulary)
 COMPARISON_SIZES = {"w1024": (1024, 8, 2, 128, 2816, 32000), "w2048": (2048, 16, 4, 128, 5632, 32000)}
+
+SHAPES["vuvosun-w1024"] = vuvosun(*COMPARISON_SIZES["w1024"])
+SHAPES["vuvosun-w2048"] = vuvosun(*COMPARISON_SIZES["w2048"])

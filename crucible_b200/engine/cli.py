@@ -95,9 +95,18 @@ def cmd_inspect(args) -> int:
     print(f"layers         {cfg.n_layers} (run order of {len(cfg.run_order)})")
     print(f"width          {cfg.hidden_size}")
     print(f"vocabulary     {cfg.vocab_size} ({'tied' if cfg.tie_word_embeddings else 'untied'} head)")
-    print(f"context        {cfg.max_context}")
+    from ..config.model_config import UNBOUNDED_CONTEXT
+    print("context        " + (str(cfg.max_context) if cfg.max_context < UNBOUNDED_CONTEXT
+                               else "no limit in the design (the engine's option or its page pool bounds a request)"))
+    kinds = [f"{l.mixer.kind}+{l.feed_forward.kind}" for l in cfg.layers]
+    if len(set(kinds)) > 1:
+        print(f"layer kinds    {' '.join(kinds)} ({cfg.layers[0].arrangement})")
     print(f"layer 0 mixer  {m.kind}: {m.n_heads} heads, {m.n_kv_heads} kv heads, head size "
           f"{m.head_dim}, window {m.window}")
+    for name, branch, scale in (m.option("branches") or ()):
+        print(f"  branch {name:6s} {branch.kind}: {branch.n_heads} heads, {branch.n_kv_heads} kv heads, "
+              f"head size {branch.head_dim}, window {branch.window}, scale {scale}, "
+              f"options {dict(branch.extra)}")
     print(f"layer 0 ffn    {cfg.layers[0].feed_forward.kind}: {cfg.layers[0].feed_forward.intermediate}")
     print(f"norm           {cfg.final_norm.kind} eps {cfg.final_norm.eps}")
     print(f"cache groups   {len(model.cache_groups)}; state bytes per request {model.state_bytes}")
