@@ -577,7 +577,9 @@ def run_profile_case(args):
     from crucible_b200.engine import StepEntry
     from crucible_b200.weights import write_random_model
     raw = shape(args.shape)
-    if args.layers:
+    if args.layers and isinstance(raw.get("layers"), list):
+        raw["layers"] = raw["layers"][:args.layers]          # a design that lists its layers
+    elif args.layers:
         raw["n_layer" if "n_layer" in raw else "num_hidden_layers"] = args.layers
     rng = random.Random(1)
     with tempfile.TemporaryDirectory() as tmp:
@@ -696,8 +698,9 @@ def main():
     p.add_argument("--impl", default="ours", choices=["ours", "reference", "cpu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
-    p.add_argument("--shape", default="120m", choices=sorted(SHAPE_LABEL),
-                   help="a named shape; the default is the benchmark's")
+    p.add_argument("--shape", default="120m", choices=sorted(SHAPE_LABEL) + ["vuvosun-w1024", "vuvosun-w2048"],
+                   help="a named shape; the default is the benchmark's (the vuvosun shapes: with "
+                        "--profile-case only; their numbers come from --compare vuvosun)")
     p.add_argument("--layers", type=int, default=0,
                    help="fewer layers than the shape has (both numbers are reported)")
     p.add_argument("--profile-case", default=None, choices=["prefill", "decode"],
@@ -712,6 +715,9 @@ def main():
         return run_design_comparison(args)
     if args.profile_case:
         return run_profile_case(args)
+    if args.shape not in SHAPE_LABEL:
+        print(f"bench.py: --shape {args.shape} runs with --profile-case; use --compare vuvosun for its numbers")
+        return 2
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -44,13 +44,15 @@ def test_parse_builds_the_layers_the_config_lists(name):
 
 def test_storage_follows_the_layers():
     a = DecoderModel(parse_config(cases.CASES["vu-a"]["config"]))
-    (group,) = a.cache_groups
+    group, other = a.cache_groups
     assert group.layers == (0, 2) and group.need.window == 24 and group.need.keep_first == 3
     assert group.need.head_dim == 32 and group.need.value_dim == 16
-    # per request: delta-rule matrices and convolution tails of two layers, one mLSTM memory
+    assert other.layers == (3,) and other.need.window == 9 and other.need.keep_first == 0
+    # per request: delta-rule matrices and convolution tails of three layers, one mLSTM memory
     delta = 4 * 4 * 16 * 24 + 4 * 2 * (2 * 4 * 16 + 4 * 24)
+    small = 4 * 2 * 8 * 8 + 4 * 3 * (2 * 1 * 8 + 2 * 8)
     mlstm = 4 * 2 * 16 * 32 + 4 * 2 * 16 + 16
-    assert a.state_bytes == 2 * delta + mlstm
+    assert a.state_bytes == 2 * delta + small + mlstm
     b = DecoderModel(parse_config(cases.CASES["vu-b"]["config"]))
     assert b.cache_groups == [] and b.state_bytes > 0
     c = DecoderModel(parse_config(cases.CASES["vu-c"]["config"]))

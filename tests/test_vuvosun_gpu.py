@@ -182,7 +182,7 @@ def test_window_pages_go_back_and_kept_first_pages_stay(tmp_path):
     assert table[-1] >= 0 and table[-2] >= 0
     engine.cache.check_invariants()
     engine.finish("a")
-    assert engine.cache.free_pages(0) == 20
+    assert engine.cache.free_pages(0) == 20 and engine.cache.free_pages(1) == 20
 
 
 @pytest.mark.parametrize("name", sorted(cases.CASES))

@@ -33,7 +33,10 @@ CASES = {
         "architecture": "Vuvosun", "vocab": 300, "width": 64, "streams": 2, "norm": {"eps": 1e-6},
         "layers": [_parallel(_left(4, 2, 32, 16, 16, 24, 3, 0.2), _right(4, 4, 16, 24, 3), 0.7, 1.3, 96),
                    _mlstm(2, 16, 32, 10.0, 0),
-                   _parallel(_left(4, 2, 32, 16, 16, 24, 3, 0.2), _right(4, 4, 16, 24, 3), 0.7, 1.3, 96)]}),
+                   _parallel(_left(4, 2, 32, 16, 16, 24, 3, 0.2), _right(4, 4, 16, 24, 3), 0.7, 1.3, 96),
+                   # a layer whose attention differs (window, heads, sizes, all features turned): its
+                   # keys live in pages of their own; no feed-forward
+                   _parallel(_left(2, 1, 16, 16, 16, 9, 0, 0.3, 300.0), _right(2, 1, 8, 8, 4), -0.5, 1.0, 0)]}),
     # no layer keeps keys: the engine has no page pool at all; one stream
     "vu-b": dict(seed=4, page_tokens=32, config={
         "architecture": "Vuvosun", "vocab": 211, "width": 96, "streams": 1, "norm": {"eps": 1e-5},
