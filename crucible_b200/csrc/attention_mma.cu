@@ -839,24 +839,25 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttnParams p
     const int hd = p.head_dim, stride = hd + 2;
     const float* base = p.partial + (((size_t)req * p.n_kv_heads + kv_head) * p.n_chunks * max_rows + row) * stride;
     const size_t chunk_stride = (size_t)max_rows * stride;
-    float top = -INFINITY;
-    for (int c = 0; c < p.n_chunks; ++c) top = fmaxf(top, base[c * chunk_stride + hd]);
+    // lane c holds share c's maximum and sum (at most 32 shares)
+    const float m_c = lane < p.n_chunks ? base[lane * chunk_stride + hd] : -INFINITY;
+    const float l_c = lane < p.n_chunks ? base[lane * chunk_stride + hd + 1] : 0.f;
+    float top = cb_warp_max(m_c);
     const int head = kv_head * n_rep + row % n_rep;
     float sk = -INFINITY;
     if (p.sinks != nullptr) {
         sk = p.sinks[head] * LOG2E;
         top = fmaxf(top, sk);
     }
-    float l = p.sinks != nullptr ? exp2f(sk - top) : 0.f;
+    const float w_c = m_c == -INFINITY ? 0.f : exp2f(m_c - top);
+    float l = cb_warp_sum(l_c * w_c) + (p.sinks != nullptr ? exp2f(sk - top) : 0.f);
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 4
     for (int c = 0; c < p.n_chunks; ++c) {
         const float* part = base + c * chunk_stride;
-        const float m = part[hd];
-        if (m == -INFINITY) continue;
-        const float w = exp2f(m - top);
-        l += part[hd + 1] * w;
+        const float w = __shfl_sync(0xffffffffu, w_c, c);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int f = lane + 32 * i;
@@ -1065,7 +1066,7 @@ CB_EXPORT int cb_attention_mma_sink(const void* q, int q_stride, void* out, int 
     if (n_chunks > 1) {
         // the key tiles of every request's (single) row tile in n_chunks shares, then a merge;
         // partial: n_requests * n_kv_heads * n_chunks * max_rows * (head_dim + 2) floats
-        if (partial == nullptr || max_rows > 64) return CB_ERR_UNSUPPORTED;
+        if (partial == nullptr || max_rows > 64 || n_chunks > 32) return CB_ERR_UNSUPPORTED;
         p.chunk_keys = max_rows;
         if (head_dim <= 16) return launch_tiles_split<16>(p, n_requests, max_rows, s);
         if (head_dim <= 32) return launch_tiles_split<32>(p, n_requests, max_rows, s);

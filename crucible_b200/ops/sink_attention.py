@@ -86,7 +86,7 @@ def _tensor_cores(q, gate, out, sinks, n_heads, n_kv_heads, key_dim, value_dim, 
     if max_rows <= 64:
         reach = host.context_bucket if window is None else min(window + 64, host.context_bucket)
         tiles = -(-reach // 64) + (-(-keep_first // 64) if window is not None else 0)
-        n_chunks = max(1, min(tiles // 2, 296 // max(1, n_kv_heads * ctx.n_requests)))
+        n_chunks = max(1, min(tiles // 2, 296 // max(1, n_kv_heads * ctx.n_requests), 32))
         if n_chunks > 1:
             partial = ctx.scratch("sink_attention.partial",
                                   (ctx.n_requests * n_kv_heads * n_chunks * max_rows * (key_dim + 2),),
