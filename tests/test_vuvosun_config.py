@@ -125,3 +125,20 @@ def test_plain_rules():
     v = torch.ones(1, 1, 2, dtype=torch.float64)
     out = plain.attend(q, k, v, torch.tensor([0]), torch.zeros(1, dtype=torch.float64), 1.0, None, 0)
     assert torch.allclose(out, torch.full((1, 1, 2), 0.5, dtype=torch.float64))
+
+
+def test_cache_pages_may_hold_values_of_another_size():
+    from crucible_b200.engine.context import CacheStorage
+    same = CacheStorage(2, 5, 8, 3, 16, torch.float32, "cpu")
+    assert same.keys(1).shape == (5, 3, 8, 16) and same.values(1).shape == (5, 3, 8, 16)
+    other = CacheStorage(2, 5, 8, 3, 16, torch.float32, "cpu", value_dim=40)
+    assert other.keys(1).shape == (5, 3, 8, 16) and other.values(1).shape == (5, 3, 8, 40)
+    assert other.keys(0).data_ptr() != other.keys(1).data_ptr()
+
+
+def test_named_shapes_of_the_design_parse():
+    from crucible_b200.config import shape
+    for name in ("vuvosun-w1024", "vuvosun-w2048"):
+        cfg = parse_config(shape(name))
+        assert cfg.architecture == "Vuvosun" and len(cfg.layers) == 4
+        assert [l.mixer.kind for l in cfg.layers] == ["mlstm", "parallel", "mlstm", "parallel"]

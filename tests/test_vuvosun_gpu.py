@@ -222,3 +222,23 @@ def test_config_values_that_another_model_makes_equal_or_absent(tmp_path):
         got = helpers.collect(trace, str(tmp_path / dtype), 97)
         for key, row in got.items():
             assert helpers.relative_error(row, ref[key[0]][key[1]]) <= TOLERANCE[dtype], (dtype, key)
+
+
+def test_a_design_without_a_context_limit_is_bounded_by_the_engine(tmp_path):
+    from crucible_b200.engine.engine import Engine, EngineOptions, StepEntry, StepError
+    model_dir = cases.make_folder(tmp_path, "vu-b")
+    engine = Engine(model_dir, EngineOptions(dtype="float32", page_tokens=32, n_pages=4, max_requests=2))
+    assert engine.max_context == 128                      # what its pages hold
+    tokens = helpers.random_tokens(211, 129, 1)
+    with pytest.raises(StepError):
+        engine.step([StepEntry("a", tokens, [])])
+    assert not engine.has_request("a") and engine.cache.slots.free_slots == 2
+    engine.step([StepEntry("a", tokens[:128], [127])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry("a", tokens[128:], [0])])
+    assert engine.held_tokens("a") == 128
+    bounded = Engine(model_dir, EngineOptions(dtype="float32", page_tokens=32, n_pages=8, max_requests=2,
+                                              max_context=40))
+    assert bounded.max_context == 40
+    with pytest.raises(StepError):
+        bounded.step([StepEntry("a", tokens[:41], [])])
