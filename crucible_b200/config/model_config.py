@@ -42,6 +42,9 @@ class PositionSpec:
     rotary_dim: int        # how many leading features of a head are rotated
     theta: float
     max_positions: int
+    # options of encodings that stretch their frequencies, as (key, value) pairs:
+    # factor, original, fast, slow
+    scaling: Optional[Tuple[Tuple[str, float], ...]] = None
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,124 @@
+// Attention over a cached latent: a token leaves one row [c | k_rot] in the pages, c the
+// RMS-normed latent of `rank` features and k_rot a rotated key part of `rot` features that all
+// heads share.  With each head's key matrix folded into its query
+//   q'[h] = [ W_uk[h]^T q_plain[h] | rotate(q_rot[h]) ],
+// the head's scores over the cache are q'[h] . [c | k_rot], and with the cached row also taken
+// as the value, the first `rank` features of the result are sum_j p_j c_j, which the head's
+// value matrix takes to its output.  So the attention itself is the paged attention of one
+// shared key/value head of size rank + rot.  The kernels here are what surrounds it:
+//
+//   prepare   per token: RMS norm (fp32) of the latent with its gain, the rotation of the
+//             shared key part, the row's write into its page; and the rotation of every
+//             head's q_rot into the last `rot` columns of q'.
+//   head gate per (token, head): the head's output times sigmoid(logit).
+//
+// Rotation: feature i pairs with i + rot/2; the angle is fp32(position) * freq[i] as an fp32
+// product, cos and sin (fp32) times `mscale`.
+#define CB_PDL_BIT 15      // this file's bit in CRUCIBLE_PDL
+#include "common.cuh"
+
+namespace {
+
+// dkv: T rows [rank + rot]; q: T rows [H][dim + rot]; qx: T rows [H][rank + rot] (only the
+// last rot columns of every head are written here); pages: T [page][1][page_tokens][rank + rot].
+template <typename T>
+__global__ void latent_prepare_kernel(const T* __restrict__ dkv, int dkv_stride, const T* __restrict__ q,
+                                      int q_stride, T* __restrict__ qx, int qx_stride,
+                                      const float* __restrict__ gain, const float* __restrict__ freq,
+                                      float mscale, float eps, const int* __restrict__ positions,
+                                      const int* __restrict__ row_request,
+                                      const int* __restrict__ block_table, int table_stride,
+                                      T* __restrict__ pages, int n_heads, int dim, int rank, int rot,
+                                      int page_tokens, int write) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rot >> 1;
+    const T* src = dkv + (size_t)t * dkv_stride;
+    if (write) {
+        const int page = block_table[(size_t)row_request[t] * table_stride + pos / page_tokens];
+        T* dst = pages + ((size_t)page * page_tokens + (pos % page_tokens)) * (rank + rot);
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+            const float v = cb_to_float(src[i]);
+            ss = fmaf(v, v, ss);
+        }
+        const float r = 1.0f / sqrtf(cb_block_sum(ss, scratch) / (float)rank + eps);
+        for (int i = threadIdx.x; i < rank; i += blockDim.x)
+            dst[i] = cb_from_float<T>(cb_to_float(src[i]) * r * gain[i]);
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float sn, cs;
+            sincosf((float)pos * freq[i], &sn, &cs);
+            sn *= mscale; cs *= mscale;
+            const float u = cb_to_float(src[rank + i]), v = cb_to_float(src[rank + half + i]);
+            dst[rank + i] = cb_from_float<T>(u * cs - v * sn);
+            dst[rank + half + i] = cb_from_float<T>(v * cs + u * sn);
+        }
+    }
+    for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        float sn, cs;
+        sincosf((float)pos * freq[j], &sn, &cs);
+        sn *= mscale; cs *= mscale;
+        const T* qr = q + (size_t)t * q_stride + (size_t)h * (dim + rot) + dim;
+        T* dq = qx + (size_t)t * qx_stride + (size_t)h * (rank + rot) + rank;
+        const float u = cb_to_float(qr[j]), v = cb_to_float(qr[half + j]);
+        dq[j] = cb_from_float<T>(u * cs - v * sn);
+        dq[half + j] = cb_from_float<T>(v * cs + u * sn);
+    }
+}
+
+// x[t][h][:] *= sigmoid(logit[t][h])
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, int x_stride, const float* __restrict__ logit,
+                                 int logit_stride, int n_rows, int n_heads, int E) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < n_heads * E; i += blockDim.x) {
+        const float g = 1.0f / (1.0f + expf(-logit[(size_t)t * logit_stride + i / E]));
+        T* at = x + (size_t)t * x_stride + i;
+        *at = cb_from_float<T>(cb_to_float(*at) * g);
+    }
+}
+
+}  // namespace
+
+CB_EXPORT int cb_latent_prepare(const void* dkv, int dkv_stride, const void* q, int q_stride, void* qx,
+                                int qx_stride, int dtype, const float* gain, const float* freq,
+                                float mscale, float eps, const int* positions, const int* row_request,
+                                const int* block_table, int table_stride, void* pages, int n_rows,
+                                int n_heads, int dim, int rank, int rot, int page_tokens, int write,
+                                void* stream) {
+    if (n_rows <= 0) return 0;
+    if (rot < 0 || (rot & 1) || rank <= 0) return CB_ERR_UNSUPPORTED;
+    const dim3 grid(n_rows), block(rank >= 512 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(latent_prepare_kernel<float>, grid, block, 0, s, (const float*)dkv, dkv_stride,
+                  (const float*)q, q_stride, (float*)qx, qx_stride, gain, freq, mscale, eps, positions,
+                  row_request, block_table, table_stride, (float*)pages, n_heads, dim, rank, rot,
+                  page_tokens, write);
+    else
+        cb_launch(latent_prepare_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)dkv,
+                  dkv_stride, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)qx, qx_stride, gain, freq,
+                  mscale, eps, positions, row_request, block_table, table_stride, (__nv_bfloat16*)pages,
+                  n_heads, dim, rank, rot, page_tokens, write);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_head_gate(void* x, int x_stride, int dtype, const float* logit, int logit_stride,
+                           int n_rows, int n_heads, int E, void* stream) {
+    if (n_rows <= 0) return 0;
+    const dim3 grid(n_rows), block(n_heads * E >= 1024 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(head_gate_kernel<float>, grid, block, 0, s, (float*)x, x_stride, logit, logit_stride,
+                  n_rows, n_heads, E);
+    else
+        cb_launch(head_gate_kernel<__nv_bfloat16>, grid, block, 0, s, (__nv_bfloat16*)x, x_stride, logit,
+                  logit_stride, n_rows, n_heads, E);
+    return cb_last_error();
+}

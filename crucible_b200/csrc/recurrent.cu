@@ -1,6 +1,7 @@
 // Mixers that carry a matrix of fixed size per head from token to token instead of
-// a cache of keys: the gated delta rule and the matrix memory with exponential gates
-// (mLSTM).  Per request and head the state is S [D][E] in fp32 (mLSTM also n [D] and
+// a cache of keys: the gated delta rule, the matrix memory with exponential gates
+// (mLSTM), the wkv rule with a decay per key channel and a bonus for the current token,
+// and the state-space rule with one decay per head (Mamba-2).  Per request and head the state is S [D][E] in fp32 (mLSTM also n [D] and
 // a running maximum m); it lives in the request's state slot and is read at the
 // start of a step and written at its end, so a prompt may be cut anywhere.
 //
@@ -9,6 +10,10 @@
 //   mLSTM, per token:       m' = max(f + m, i);  a = exp(f + m - m');  b = exp(i - m');
 //                           S <- a S + b k v^T;  n <- a n + b k;
 //                           o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+//   wkv, per token:         o = (S + diag(u) k v^T)^T r;  S <- diag(w) S + k v^T
+//                           (w a vector over the key channels, u a constant per head)
+//   state space, per token: S <- a S + (dt k) v^T;  o = S^T q + skip v
+//                           (a, dt numbers per head and token, skip a constant per head)
 //
 // Kernels: the preparation of a step's rows (for the delta rule: a short causal
 // convolution over time per channel, whose last taps - 1 inputs are state too,
@@ -26,7 +31,7 @@
 
 namespace {
 
-constexpr int RULE_DELTA = 0, RULE_MLSTM = 1;
+constexpr int RULE_DELTA = 0, RULE_MLSTM = 1, RULE_WKV = 2, RULE_SSD = 3;
 constexpr int GATE_SILU = 0, GATE_SIGMOID = 1;
 constexpr int THREADS = 128;      // of a recurrence block: 128 / LANES columns of S
 constexpr int CHUNK = 16;         // tokens staged at a time
@@ -168,13 +173,17 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
     const float* __restrict__ sc0, const float* __restrict__ sc1,
     const int* __restrict__ req_row_start, const int* __restrict__ req_state_slot,
     unsigned char* state, long slot_stride, long s_off, long n_off, long m_off,
-    float* __restrict__ out, int n_heads, int n_qk_heads, int D, int E) {
+    float* __restrict__ out, int n_heads, int n_qk_heads, int D, int E, int w_off,
+    const float* __restrict__ per_head) {
+    // w_off: wkv's decay vectors in the rows of qkv (one of D per head); per_head: wkv's bonus
+    // u [H][D], the state-space rule's skip [H]
     cb_pdl_trigger();
     cb_pdl_wait();
     constexpr int COLS = THREADS / LANES;
     constexpr int PAD = P == 4 ? 8 : 4;       // the parts' 16-byte reads then fall on different banks
     constexpr int PITCH = LANES * (P + PAD);
-    constexpr int BUF = CHUNK * (2 * PITCH + COLS) + 2 * CHUNK;      // floats of one stage
+    constexpr int NVEC = RULE == RULE_WKV ? 3 : 2;      // staged vectors of D per token: k, q (, w)
+    constexpr int BUF = CHUNK * (NVEC * PITCH + COLS) + 2 * CHUNK;      // floats of one stage
     extern __shared__ __align__(16) float stage[];
     const int r = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * COLS;
     const int g = head / (n_heads / n_qk_heads);
@@ -195,17 +204,20 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
         const int d = part * P + i;
         s[i] = (live && d < D) ? S[(size_t)d * E + col] : 0.f;
         n[i] = (RULE == RULE_MLSTM && d < D) ? N[d] : 0.f;
+        if (RULE == RULE_WKV) n[i] = d < D ? per_head[(size_t)head * D + d] : 0.f;      // the bonus u
     }
+    const float skip = RULE == RULE_SSD ? per_head[head] : 0.f;
     if (RULE == RULE_MLSTM) m = *M;
     __syncthreads();
     // 16-byte copies if every row of q and k starts on a 16-byte boundary
-    const bool vec = ((C | q_off | k_off | D) & 3) == 0;
+    const bool vec = ((C | q_off | k_off | D | (RULE == RULE_WKV ? w_off : 0)) & 3) == 0;
     // a chunk's q, k, v and gates on their way into one of the two stages (asynchronous
     // copies: the next chunk travels while this one is worked on)
     auto fetch = [&](int base, int buf) {
         float* sk = stage + buf * BUF;
         float* sq = sk + CHUNK * PITCH;
-        float* sv = sq + CHUNK * PITCH;
+        float* sv = sq + (NVEC - 1) * CHUNK * PITCH;
+        float* sw = sq + CHUNK * PITCH;                     // wkv only
         float* s0 = sv + CHUNK * COLS;
         float* s1 = s0 + CHUNK;
         const int cnt = min(CHUNK, row1 - base);
@@ -217,6 +229,7 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
                 const int at = tt * PITCH + d + (d / P) * PAD;
                 cp_async<16>(sk + at, src + k_off);
                 cp_async<16>(sq + at, src + q_off);
+                if (RULE == RULE_WKV) cp_async<16>(sw + at, src + w_off);
             }
         } else {
             for (int i = threadIdx.x; i < cnt * D; i += blockDim.x) {
@@ -225,6 +238,7 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
                 const int at = tt * PITCH + d + (d / P) * PAD;
                 cp_async<4>(sk + at, src + k_off);
                 cp_async<4>(sq + at, src + q_off);
+                if (RULE == RULE_WKV) cp_async<4>(sw + at, src + w_off);
             }
         }
         for (int i = threadIdx.x; i < cnt * COLS; i += blockDim.x) {
@@ -232,7 +246,7 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
             if (col0 + c < E)
                 cp_async<4>(sv + i, qkv + (size_t)(base + tt) * C + v_off + (size_t)head * E + col0 + c);
         }
-        if (threadIdx.x < cnt) {
+        if (RULE != RULE_WKV && threadIdx.x < cnt) {
             cp_async<4>(s0 + threadIdx.x, sc0 + (size_t)(base + threadIdx.x) * n_heads + head);
             cp_async<4>(s1 + threadIdx.x, sc1 + (size_t)(base + threadIdx.x) * n_heads + head);
         }
@@ -258,7 +272,8 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
         __syncthreads();
         const float* sk = stage + buf * BUF;
         const float* sq = sk + CHUNK * PITCH;
-        const float* sv = sq + CHUNK * PITCH;
+        const float* sv = sq + (NVEC - 1) * CHUNK * PITCH;
+        const float* sw = sq + CHUNK * PITCH;
         const float* s0 = sv + CHUNK * COLS;
         const float* s1 = s0 + CHUNK;
 #pragma unroll 4
@@ -303,6 +318,41 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
                 for (int i = 0; i < P; ++i) k_prev[i] = kk[i];
                 g_prev = decay;
                 u_prev = u;
+            } else if (RULE == RULE_WKV || RULE == RULE_SSD) {
+                // As below: the update needs no sum over a column; a token's sum is reduced and
+                // stored under the next token's pass.
+                float oc[4] = {0.f, 0.f, 0.f, 0.f};
+                if (RULE == RULE_WKV) {
+                    const float4* w4 = reinterpret_cast<const float4*>(sw + tt * PITCH + part * (P + PAD));
+                    float ww[P];
+#pragma unroll
+                    for (int j = 0; j < P / 4; ++j) {
+                        const float4 a = w4[j];
+                        ww[4 * j] = a.x; ww[4 * j + 1] = a.y; ww[4 * j + 2] = a.z; ww[4 * j + 3] = a.w;
+                    }
+#pragma unroll
+                    for (int i = 0; i < P; ++i) {
+                        const float kv = kk[i] * v;
+                        oc[i & 3] = fmaf(fmaf(n[i], kv, s[i]), qq[i], oc[i & 3]);
+                        s[i] = fmaf(ww[i], s[i], kv);
+                    }
+                } else {
+                    const float a = s0[tt], dv = s1[tt] * v;
+#pragma unroll
+                    for (int i = 0; i < P; ++i) {
+                        s[i] = fmaf(kk[i], dv, a * s[i]);
+                        oc[i & 3] = fmaf(s[i], qq[i], oc[i & 3]);
+                    }
+                }
+                if (pending) {
+#pragma unroll
+                    for (int x = 1; x < LANES; x <<= 1) p_o += __shfl_xor_sync(0xffffffffu, p_o, x);
+                    if (live && part == 0) out[p_at] = p_o + p_n;
+                }
+                p_o = (oc[0] + oc[1]) + (oc[2] + oc[3]);
+                p_n = skip * v;
+                p_at = out_at;
+                pending = true;
             } else {
                 // The state's update needs no sum over a column, so tokens follow one another
                 // without waiting for a shuffle: a token's sums are reduced, divided and stored
@@ -340,6 +390,10 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
     if (RULE == RULE_DELTA) {
 #pragma unroll
         for (int i = 0; i < P; ++i) s[i] = fmaf(k_prev[i], u_prev, g_prev * s[i]);      // the last token's write
+    } else if ((RULE == RULE_WKV || RULE == RULE_SSD) && pending) {
+#pragma unroll
+        for (int x = 1; x < LANES; x <<= 1) p_o += __shfl_xor_sync(0xffffffffu, p_o, x);
+        if (live && part == 0) out[p_at] = p_o + p_n;
     } else if (pending) {
 #pragma unroll
         for (int x = 1; x < LANES; x <<= 1) {
@@ -355,6 +409,125 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
         if (RULE == RULE_MLSTM && blockIdx.z == 0 && col == 0 && d < D) N[d] = n[i];
     }
     if (RULE == RULE_MLSTM && blockIdx.z == 0 && threadIdx.x == 0) *M = m;
+}
+
+// ---- wkv: the mixes of a token with the token before it ------------------------------------
+// h: T rows [rows][width].  mu: fp32 [n_mix][width].  out: T [n_mix][rows][width]:
+//   out[s][t] = h[t] + (h[t-1] - h[t]) * mu[s]      (fp32 arithmetic, rounded once)
+// h[t-1] of a portion's first row is the request's state (fp32 [width], zeros at a sequence's
+// start); the block of that row reads it and then leaves the portion's last row there.
+template <typename T>
+__global__ void shift_mix_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ mu,
+                                 int n_mix, const int* __restrict__ row_request,
+                                 const int* __restrict__ req_row_start,
+                                 const int* __restrict__ req_state_slot, unsigned char* state,
+                                 long slot_stride, long prev_off, T* __restrict__ out, int n_rows,
+                                 int width) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int t = blockIdx.x;
+    const int r = row_request[t];
+    const int row0 = req_row_start[r], row1 = req_row_start[r + 1];
+    float* kept = state_at(state, slot_stride, req_state_slot[r], prev_off);
+    const T* cur = h + (size_t)t * h_stride;
+    const T* before = t > row0 ? h + (size_t)(t - 1) * h_stride : nullptr;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float x = cb_to_float(cur[i]);
+        const float d = (before != nullptr ? cb_to_float(before[i]) : kept[i]) - x;
+        for (int s = 0; s < n_mix; ++s)
+            out[((size_t)s * n_rows + t) * width + i] = cb_from_float<T>(fmaf(d, mu[(size_t)s * width + i], x));
+    }
+    if (t == row0) {
+        // each thread rewrites only the entries it has read itself
+        const T* last = h + (size_t)(row1 - 1) * h_stride;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) kept[i] = cb_to_float(last[i]);
+    }
+}
+
+// ---- wkv: r, k, v to fp32 and the decay w = exp(-exp(logit + w0)) ---------------------------
+// rkv: T [3][rows][H*D] (r, k, v one after the other); logit: fp32 [rows][H*D]; qkv: fp32
+// [rows][4*H*D] = [r | k | v | w].
+template <typename T>
+__global__ void wkv_prepare_kernel(const T* __restrict__ rkv, long plane_stride,
+                                   const float* __restrict__ logit, const float* __restrict__ w0,
+                                   float* __restrict__ qkv, int HD) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int t = blockIdx.x;
+    float* dst = qkv + (size_t)t * 4 * HD;
+    for (int c = threadIdx.x; c < 3 * HD; c += blockDim.x) {
+        const int plane = c / HD;
+        dst[c] = cb_to_float(rkv[(size_t)plane * plane_stride + (size_t)t * HD + (c - plane * HD)]);
+    }
+    for (int c = threadIdx.x; c < HD; c += blockDim.x)
+        dst[3 * HD + c] = expf(-expf(logit[(size_t)t * HD + c] + w0[c]));
+}
+
+// ---- state space: convolution with bias + SiLU over [x | B | C], step size and decay --------
+// proj: T rows whose columns conv_at .. conv_at + C - 1 are the convolution's channels; conv_w:
+// fp32 [C][taps], the last column meets the current token; conv_b: fp32 [C].  The request's
+// state holds the last taps - 1 inputs of every channel, oldest first, fp32 [taps-1][C].
+// gates: fp32 [rows][H] step-size logits: dt = softplus(logit + dt_bias), decay = exp(-exp(A_log) dt).
+template <typename T>
+__global__ void ssd_prepare_kernel(const T* __restrict__ proj, int proj_stride, int conv_at,
+                                   const float* __restrict__ conv_w, const float* __restrict__ conv_b,
+                                   int taps, const float* __restrict__ gates, int gates_stride,
+                                   const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                   const int* __restrict__ row_request,
+                                   const int* __restrict__ req_row_start,
+                                   const int* __restrict__ req_state_slot, unsigned char* state,
+                                   long slot_stride, long tail_off, float* __restrict__ xbc,
+                                   float* __restrict__ decay, float* __restrict__ step, int n_heads,
+                                   int C) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int t = blockIdx.x;
+    const int r = row_request[t];
+    const int first = req_row_start[r];
+    const int local = t - first;
+    const float* tail = state_at(state, slot_stride, req_state_slot[r], tail_off);
+    float* dst = xbc + (size_t)t * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = conv_b != nullptr ? conv_b[c] : 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = local - (taps - 1) + j;
+            const float x = src >= 0 ? cb_to_float(proj[(size_t)(first + src) * proj_stride + conv_at + c])
+                                     : tail[(size_t)(taps - 1 + src) * C + c];
+            acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+        }
+        dst[c] = silu_f(acc);
+    }
+    for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
+        const float dt = softplus_f(gates[(size_t)t * gates_stride + h] + dt_bias[h]);
+        step[(size_t)t * n_heads + h] = dt;
+        decay[(size_t)t * n_heads + h] = expf(-expf(a_log[h]) * dt);
+    }
+}
+
+// ---- output gate, then RMS norm in equal parts of a row, then gain ---------------------------
+// y: fp32 [rows][width]; gate: T rows; out[t] = unit_rms_per_part(y[t] * silu(gate[t])) * gain.
+// One block per (row, part); the block size is a function of the part's width alone.
+template <typename T>
+__global__ void gate_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate,
+                                       int gate_stride, const float* __restrict__ gain,
+                                       T* __restrict__ out, int out_stride, int width, int parts,
+                                       float eps) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    __shared__ float scratch[32];
+    const int t = blockIdx.x / parts, part = blockIdx.x - t * parts;
+    const int n = width / parts, at = part * n;
+    const float* src = y + (size_t)t * width + at;
+    const T* g = gate + (size_t)t * gate_stride + at;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = src[i] * silu_f(cb_to_float(g[i]));
+        ss = fmaf(v, v, ss);
+    }
+    const float r = 1.0f / sqrtf(cb_block_sum(ss, scratch) / (float)n + eps);
+    T* dst = out + (size_t)t * out_stride + at;
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        dst[i] = cb_from_float<T>(src[i] * silu_f(cb_to_float(g[i])) * r * gain[at + i]);
 }
 
 // ---- per-head RMS norm, gain and output gate ----------------------------------------------
@@ -389,10 +562,11 @@ template <int P, int LANES, int RULE>
 int launch_memory_as(const float* qkv, int C, int q_off, int k_off, int v_off, const float* sc0,
                      const float* sc1, const int* req_row_start, const int* req_state_slot,
                      unsigned char* state, long slot_stride, long s_off, long n_off, long m_off, float* out,
-                     int n_requests, int n_heads, int n_qk_heads, int D, int E, cudaStream_t s) {
-    constexpr int COLS = THREADS / LANES, PAD = P == 4 ? 8 : 4;
+                     int n_requests, int n_heads, int n_qk_heads, int D, int E, int w_off,
+                     const float* per_head, cudaStream_t s) {
+    constexpr int COLS = THREADS / LANES, PAD = P == 4 ? 8 : 4, NVEC = RULE == RULE_WKV ? 3 : 2;
     const dim3 grid(n_requests, n_heads, (E + COLS - 1) / COLS), block(THREADS);
-    const size_t smem = 2 * (size_t)(CHUNK * (2 * LANES * (P + PAD) + COLS) + 2 * CHUNK) * sizeof(float);
+    const size_t smem = 2 * (size_t)(CHUNK * (NVEC * LANES * (P + PAD) + COLS) + 2 * CHUNK) * sizeof(float);
     if (smem > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
@@ -404,7 +578,7 @@ int launch_memory_as(const float* qkv, int C, int q_off, int k_off, int v_off, c
     }
     cb_launch(matrix_memory_kernel<P, LANES, RULE>, grid, block, smem, s, qkv, C, q_off, k_off, v_off, sc0,
               sc1, req_row_start, req_state_slot, state, slot_stride, s_off, n_off, m_off, out, n_heads,
-              n_qk_heads, D, E);
+              n_qk_heads, D, E, w_off, per_head);
     return cb_last_error();
 }
 
@@ -416,11 +590,13 @@ template <int RULE>
 int launch_memory(const float* qkv, int C, int q_off, int k_off, int v_off, const float* sc0,
                   const float* sc1, const int* req_row_start, const int* req_state_slot,
                   unsigned char* state, long slot_stride, long s_off, long n_off, long m_off, float* out,
-                  int n_requests, int n_heads, int n_qk_heads, int D, int E, cudaStream_t s) {
+                  int n_requests, int n_heads, int n_qk_heads, int D, int E, int w_off,
+                  const float* per_head, cudaStream_t s) {
 #define CB_MEM(PP, LL)                                                                              \
     return launch_memory_as<PP, LL, RULE>(qkv, C, q_off, k_off, v_off, sc0, sc1, req_row_start,     \
                                           req_state_slot, state, slot_stride, s_off, n_off, m_off,  \
-                                          out, n_requests, n_heads, n_qk_heads, D, E, s)
+                                          out, n_requests, n_heads, n_qk_heads, D, E, w_off,        \
+                                          per_head, s)
     if (D <= 32) CB_MEM(4, 8);
     if (D <= 64) CB_MEM(8, 8);
     if (D <= 128) CB_MEM(16, 8);
@@ -491,25 +667,30 @@ CB_EXPORT int cb_mlstm_prepare(const void* proj, int proj_stride, int dtype, con
     return cb_last_error();
 }
 
-// rule 0: the delta rule (sc0 decay, sc1 beta); rule 1: mLSTM (sc0 log keep, sc1 log in).
+// rule 0: the delta rule (sc0 decay, sc1 beta); rule 1: mLSTM (sc0 log keep, sc1 log in);
+// rule 2: wkv (decay vectors at w_off in the rows, per_head the bonus [H][D]);
+// rule 3: state space (sc0 decay, sc1 step size, per_head the skip [H]).
 CB_EXPORT int cb_matrix_memory(int rule, const float* qkv, int C, int q_off, int k_off, int v_off,
                                const float* sc0, const float* sc1, const int* req_row_start,
                                const int* req_state_slot, void* state, long slot_stride, long s_off,
                                long n_off, long m_off, float* out, int n_requests, int n_heads,
-                               int n_qk_heads, int key_dim, int value_dim, void* stream) {
+                               int n_qk_heads, int key_dim, int value_dim, int w_off,
+                               const float* per_head, void* stream) {
     if (n_requests <= 0) return 0;
     if (n_heads % n_qk_heads != 0) return CB_ERR_UNSUPPORTED;
+    if ((rule == RULE_WKV || rule == RULE_SSD) && per_head == nullptr) return CB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (rule == RULE_DELTA)
-        return launch_memory<RULE_DELTA>(qkv, C, q_off, k_off, v_off, sc0, sc1, req_row_start,
-                                         req_state_slot, (unsigned char*)state, slot_stride, s_off,
-                                         n_off, m_off, out, n_requests, n_heads, n_qk_heads, key_dim,
-                                         value_dim, s);
-    if (rule == RULE_MLSTM)
-        return launch_memory<RULE_MLSTM>(qkv, C, q_off, k_off, v_off, sc0, sc1, req_row_start,
-                                         req_state_slot, (unsigned char*)state, slot_stride, s_off,
-                                         n_off, m_off, out, n_requests, n_heads, n_qk_heads, key_dim,
-                                         value_dim, s);
+#define CB_RULE(RR)                                                                                  \
+    if (rule == RR)                                                                                  \
+        return launch_memory<RR>(qkv, C, q_off, k_off, v_off, sc0, sc1, req_row_start,               \
+                                 req_state_slot, (unsigned char*)state, slot_stride, s_off, n_off,   \
+                                 m_off, out, n_requests, n_heads, n_qk_heads, key_dim, value_dim,    \
+                                 w_off, per_head, s)
+    CB_RULE(RULE_DELTA);
+    CB_RULE(RULE_MLSTM);
+    CB_RULE(RULE_WKV);
+    CB_RULE(RULE_SSD);
+#undef CB_RULE
     return CB_ERR_UNSUPPORTED;
 }
 
@@ -533,5 +714,76 @@ CB_EXPORT int cb_head_norm_gate(const float* o, const float* gain, int gain_head
         if (gate_kind == GATE_SILU) CB_HNG(__nv_bfloat16, GATE_SILU); else CB_HNG(__nv_bfloat16, GATE_SIGMOID);
     }
 #undef CB_HNG
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_shift_mix(const void* h, int h_stride, int dtype, const float* mu, int n_mix,
+                           const int* row_request, const int* req_row_start, const int* req_state_slot,
+                           void* state, long slot_stride, long prev_off, void* out, int n_rows, int width,
+                           void* stream) {
+    if (n_rows <= 0) return 0;
+    const dim3 grid(n_rows), block(width >= 1024 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(shift_mix_kernel<float>, grid, block, 0, s, (const float*)h, h_stride, mu, n_mix,
+                  row_request, req_row_start, req_state_slot, (unsigned char*)state, slot_stride, prev_off,
+                  (float*)out, n_rows, width);
+    else
+        cb_launch(shift_mix_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)h, h_stride, mu,
+                  n_mix, row_request, req_row_start, req_state_slot, (unsigned char*)state, slot_stride,
+                  prev_off, (__nv_bfloat16*)out, n_rows, width);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_wkv_prepare(const void* rkv, long rkv_stride, int dtype, const float* logit,
+                             const float* w0, float* qkv, int n_rows, int HD, void* stream) {
+    if (n_rows <= 0) return 0;
+    const dim3 grid(n_rows), block(HD >= 1024 ? 512 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(wkv_prepare_kernel<float>, grid, block, 0, s, (const float*)rkv, rkv_stride, logit, w0,
+                  qkv, HD);
+    else
+        cb_launch(wkv_prepare_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)rkv,
+                  rkv_stride, logit, w0, qkv, HD);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_ssd_prepare(const void* proj, int proj_stride, int conv_at, int dtype,
+                             const float* conv_w, const float* conv_b, int taps, const float* gates,
+                             int gates_stride, const float* a_log, const float* dt_bias,
+                             const int* row_request, const int* req_row_start, const int* req_state_slot,
+                             void* state, long slot_stride, long tail_off, float* xbc, float* decay,
+                             float* step, int n_rows, int n_heads, int C, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (taps < 1) return CB_ERR_UNSUPPORTED;
+    const dim3 grid(n_rows), block(C <= 256 ? 128 : (C >= 2048 ? 1024 : (C / 2 + 31) / 32 * 32));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(ssd_prepare_kernel<float>, grid, block, 0, s, (const float*)proj, proj_stride, conv_at,
+                  conv_w, conv_b, taps, gates, gates_stride, a_log, dt_bias, row_request, req_row_start,
+                  req_state_slot, (unsigned char*)state, slot_stride, tail_off, xbc, decay, step, n_heads, C);
+    else
+        cb_launch(ssd_prepare_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)proj,
+                  proj_stride, conv_at, conv_w, conv_b, taps, gates, gates_stride, a_log, dt_bias,
+                  row_request, req_row_start, req_state_slot, (unsigned char*)state, slot_stride, tail_off,
+                  xbc, decay, step, n_heads, C);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_gate_group_norm(const float* y, const void* gate, int gate_stride, const float* gain,
+                                 void* out, int out_stride, int dtype, int n_rows, int width, int parts,
+                                 float eps, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (parts <= 0 || width % parts) return CB_ERR_UNSUPPORTED;
+    const int n = width / parts;
+    const dim3 grid((unsigned)((long)n_rows * parts)), block(n >= 1024 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(gate_group_norm_kernel<float>, grid, block, 0, s, y, (const float*)gate, gate_stride, gain,
+                  (float*)out, out_stride, width, parts, eps);
+    else
+        cb_launch(gate_group_norm_kernel<__nv_bfloat16>, grid, block, 0, s, y, (const __nv_bfloat16*)gate,
+                  gate_stride, gain, (__nv_bfloat16*)out, out_stride, width, parts, eps);
     return cb_last_error();
 }

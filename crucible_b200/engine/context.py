@@ -54,13 +54,20 @@ class CacheStorage:
     elements in a row), so a head's keys are read in long runs."""
 
     def __init__(self, n_slots: int, n_pages: int, page_tokens: int, kv_heads: int,
-                 head_dim: int, dtype: torch.dtype, device, value_dim: Optional[int] = None):
+                 head_dim: int, dtype: torch.dtype, device, value_dim: Optional[int] = None,
+                 values_are_keys: bool = False):
         self.page_tokens = page_tokens
         self.n_pages = n_pages
         self.kv_heads = kv_heads
         self.head_dim = head_dim
         self.value_dim = head_dim if value_dim is None else value_dim
-        if self.value_dim == head_dim:
+        self.values_are_keys = values_are_keys
+        if values_are_keys:
+            # one row per token, read as key and as value: no pages for values
+            self.kv = None
+            self._k = self._v = torch.zeros((n_slots, n_pages, kv_heads, page_tokens, head_dim),
+                                            dtype=dtype, device=device)
+        elif self.value_dim == head_dim:
             self.kv = torch.zeros((n_slots, 2, n_pages, kv_heads, page_tokens, head_dim),
                                   dtype=dtype, device=device)
             self._k = self._v = None

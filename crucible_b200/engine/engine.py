@@ -142,7 +142,8 @@ class Engine:
         # and never another request's data.
         self.storages = [CacheStorage(len(g.layers), n_pages + 1, o.page_tokens, g.need.kv_heads,
                                       g.need.head_dim, self.dtype, self.device,
-                                      value_dim=g.need.value_dim) for g in groups]
+                                      value_dim=g.need.value_dim,
+                                      values_are_keys=g.need.values_are_keys) for g in groups]
         self.null_page = n_pages
         self.table_strides = tuple(ctx_pages for _ in groups)
         # The manager keeps every live request's table in the form that goes to the device

@@ -77,6 +77,12 @@ class DecoderModel:
         bindings: List[LayerBinding] = []
         state_offsets: Dict[int, int] = {}
         total_state = 0
+        # an embedding that remembers something of a request between steps (its last token,
+        # say) keeps it at the head of the request's state slot
+        nbytes = int(getattr(self.embedding, "state_bytes", lambda: 0)())
+        if nbytes:
+            self.embedding.state_binding = LayerBinding(state_offset=0, state_bytes=nbytes)
+            total_state = (nbytes + 15) // 16 * 16
         written = set()
         for i, entry in enumerate(self.config.run_order):
             layer = self.layers[entry.layer]

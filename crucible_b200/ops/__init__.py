@@ -156,6 +156,49 @@ def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor)
                            _c_float(eps), _stream()), "polynorm")
 
 
+ACTIVATIONS = {"relu2": 0, "tanh": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def activation(kind: str, z: torch.Tensor, out: torch.Tensor) -> None:
+    """out = act(z) elementwise (float32 arithmetic): relu2 is max(z, 0)^2."""
+    _need_cuda(z, out)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {kind!r}; known: {sorted(ACTIVATIONS)}")
+    if z.shape != out.shape or z.dim() != 2 or z.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("activation takes rows [T, F] and writes the same shape")
+    lib = build.load("activations")
+    _check(lib.cb_activation(_c_int(ACTIVATIONS[kind]), _ptr(z), _c_int(z.stride(0)), _c_int(_code(z.dtype)),
+                             _ptr(out), _c_int(out.stride(0)), _c_int(_code(out.dtype)),
+                             _c_int(z.shape[0]), _c_int(z.shape[1]), _stream()), f"activation {kind}")
+
+
+def hashed_embedding(table, bigram, positions_table, ids, ctx, state, out, scale: float, buckets: int,
+                     mul_prev: int, mul_cur: int, device_tokens=None) -> None:
+    """out[t] = table[id] * scale + bigram[hash(previous id, id)] + positions_table[position];
+    `bigram` and `positions_table` may be None.  `state`: uint8 [slots, >= 4], one int32 per
+    request (its last token + 1), read for a portion's first row and rewritten."""
+    _need_cuda(table, bigram, positions_table, ids, state, out, device_tokens)
+    if ids.dtype != torch.int32 or out.dtype != torch.float32:
+        raise KernelError("hashed_embedding takes int32 ids and a float32 output")
+    for t in (bigram, positions_table):
+        if t is not None and (t.dtype != table.dtype or t.shape[1] != table.shape[1] or not t.is_contiguous()):
+            raise KernelError("hashed_embedding: the tables share a dtype and a width")
+    if bigram is not None and bigram.shape[0] != buckets + 1:
+        raise KernelError("hashed_embedding: the bigram table has one row per bucket and one more")
+    _contig(table, "embedding table"); _contig(out, "hashed_embedding output")
+    if state is not None and (state.dtype != torch.uint8 or state.data_ptr() % 4 or state.stride(0) % 4):
+        raise KernelError("hashed_embedding: the state is a uint8 view [slots, bytes], 4-byte aligned")
+    lib = build.load("hashed_embedding")
+    _check(lib.cb_hashed_embedding(
+        _ptr(table), _ptr(bigram), _ptr(positions_table), _c_int(_code(table.dtype)), _ptr(ids),
+        _ptr(ctx.positions), _ptr(ctx.row_request), _ptr(ctx.req_row_start), _ptr(ctx.req_state_slot),
+        _ptr(state), ctypes.c_long(state.stride(0) if state is not None else 0), _ptr(out),
+        _c_int(ids.shape[0]), _c_int(table.shape[1]), _c_int(table.shape[0]), _c_float(scale),
+        _c_int(buckets), ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur),
+        _c_int(positions_table.shape[0] if positions_table is not None else 1), _ptr(device_tokens),
+        _stream()), "hashed_embedding")
+
+
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
     _need_cuda(x, rows, out)
     if x.dtype != torch.float32 or out.dtype != torch.float32 or rows.dtype != torch.int32:

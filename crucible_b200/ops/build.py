@@ -46,6 +46,10 @@ MODULES: Dict[str, List[str]] = {
     "sink_attention": ["common.cuh"],
     "recurrent": ["common.cuh"],
     "polynorm": ["common.cuh"],
+    "hashed_embedding": ["common.cuh"],
+    "activations": ["common.cuh"],
+    "latent_attention": ["common.cuh"],
+    "moe": ["common.cuh"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

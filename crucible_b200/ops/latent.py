@@ -1,0 +1,43 @@
+"""Wrappers of `csrc/latent_attention.cu`: what surrounds the attention over a cached
+latent (the latent's norm, the rotations, the write into the pages, the heads' gates)."""
+from __future__ import annotations
+
+import torch
+
+from . import KernelError, _c_float, _c_int, _check, _code, _need_cuda, _ptr, _stream, build
+
+
+def prepare(dkv, q, qx, gain, freq, mscale: float, eps: float, n_heads: int, dim: int, rank: int,
+            rot: int, ctx, cache, binding) -> None:
+    """Rows of `dkv` are [latent: rank | shared key part: rot], rows of `q` [heads, dim + rot].
+    Writes [rmsnorm(latent) * gain | rotated key part] to the token's place in the pages and the
+    rotated last `rot` features of every head of q into the last `rot` of that head in `qx`
+    [heads, rank + rot]."""
+    _need_cuda(dkv, q, qx, gain, freq)
+    if dkv.stride(1) != 1 or q.stride(1) != 1 or qx.stride(1) != 1 or not (dkv.dtype == q.dtype == qx.dtype):
+        raise KernelError("latent prepare: contiguous rows of one dtype")
+    if rot and (freq is None or freq.dtype != torch.float32 or freq.numel() * 2 != rot):
+        raise KernelError("latent prepare: freq is float32 [rot / 2]")
+    pages = cache.keys(binding.slot)
+    if pages.dtype != dkv.dtype or pages.shape[-1] != rank + rot or cache.kv_heads != 1:
+        raise KernelError("latent prepare: the pages hold one row of rank + rot features per token "
+                          "in the activations' dtype")
+    table = ctx.block_table(binding.group)
+    lib = build.load("latent_attention")
+    _check(lib.cb_latent_prepare(
+        _ptr(dkv), _c_int(dkv.stride(0)), _ptr(q), _c_int(q.stride(0)), _ptr(qx), _c_int(qx.stride(0)),
+        _c_int(_code(dkv.dtype)), _ptr(gain), _ptr(freq), _c_float(mscale), _c_float(eps),
+        _ptr(ctx.positions), _ptr(ctx.row_request), _ptr(table), _c_int(table.shape[1]), _ptr(pages),
+        _c_int(dkv.shape[0]), _c_int(n_heads), _c_int(dim), _c_int(rank), _c_int(rot),
+        _c_int(cache.page_tokens), _c_int(1 if binding.write else 0), _stream()), "latent_prepare")
+
+
+def head_gate(x, logit, n_heads: int, head_width: int) -> None:
+    """x[t, h, :] *= sigmoid(logit[t, h]) in place; `logit` float32 [rows, heads]."""
+    _need_cuda(x, logit)
+    if logit.dtype != torch.float32 or logit.stride(1) != 1 or x.stride(1) != 1 or x.shape[1] != n_heads * head_width:
+        raise KernelError("head_gate: rows [T, heads * width] and float32 logits [T, heads]")
+    lib = build.load("latent_attention")
+    _check(lib.cb_head_gate(_ptr(x), _c_int(x.stride(0)), _c_int(_code(x.dtype)), _ptr(logit),
+                            _c_int(logit.stride(0)), _c_int(x.shape[0]), _c_int(n_heads),
+                            _c_int(head_width), _stream()), "head_gate")

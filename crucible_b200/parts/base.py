@@ -51,6 +51,9 @@ class TensorDecl:
     # how the random-weights mode draws it, if not by its role's rule: ("normal", mean, std),
     # ("uniform", low, high) or ("eye", diagonal, std of the noise around it)
     init: Optional[Tuple[str, float, float]] = None
+    # axes whose size the checkpoint decides (the part reads it off the tensor at bind); the
+    # size given in `shape` is what the random-weights mode writes
+    free_dims: Tuple[int, ...] = ()
 
 
 @dataclass(frozen=True)
@@ -61,6 +64,7 @@ class CacheNeed:
     window: Optional[int] = None   # None: every earlier key stays
     value_dim: Optional[int] = None   # size of a value, if it differs from a key's
     keep_first: int = 0            # with a window: this many first tokens stay visible
+    values_are_keys: bool = False  # one row per token serves as key and as value: no value pages
 
 
 @dataclass(frozen=True)

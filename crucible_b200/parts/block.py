@@ -9,8 +9,19 @@ from .base import ARRANGEMENTS, Arrangement
 class PreNormBlock(Arrangement):
     norm_names = ("mixer_norm", "feed_forward_norm")
 
+    def __init__(self, spec, norms, mixer, feed_forward):
+        # a layer without a feed-forward sublayer (a part with `absent`) has one norm only
+        self.has_ffn = not getattr(feed_forward, "absent", False)
+        if not self.has_ffn:
+            self.norm_names = ("mixer_norm",)
+        super().__init__(spec, norms, mixer, feed_forward)
+
     def forward(self, ctx, x, binding):
         h = self._norm(ctx, self.norms["mixer_norm"], self.mixer, x)
+        if not self.has_ffn:
+            self._announce(ctx, getattr(ctx, "norm_after_layer", None), x)
+            self.mixer.forward(ctx, h, x, binding)
+            return
         self._announce(ctx, (self.norms["feed_forward_norm"], self.feed_forward), x)
         self.mixer.forward(ctx, h, x, binding)
         h = self._norm(ctx, self.norms["feed_forward_norm"], self.feed_forward, x)

@@ -62,6 +62,49 @@ class NormedStreamsEmbedding(Embedding):
         return x if self.streams is not None else x.view(token_ids.shape[0], self.width)
 
 
+class HashedPositionEmbedding(Embedding):
+    """x = table[token] * scale + bigram[(previous * mul_prev + token * mul_cur) mod buckets]
+    + positions[p].  The first token of a sequence takes the bigram row after the buckets.
+    The bigram table and the learned positions are options of the spec (`bigram`: (buckets,
+    mul_prev, mul_cur) or None; `max_positions`: rows of the position table or None).  The
+    request's last token is state: a portion's first token needs it."""
+
+    def __init__(self, spec, vocab_size: int, width: int):
+        self.vocab_size = vocab_size
+        self.width = width
+        self.scale = float(spec.option("scale", 1.0))
+        self.bigram_spec = spec.option("bigram")
+        self.max_positions = spec.option("max_positions")
+        self.table = self.bigram = self.positions = None
+        self.state_binding = None
+
+    def tensors(self):
+        out = [TensorDecl("table", (self.vocab_size, self.width))]
+        if self.bigram_spec is not None:
+            out.append(TensorDecl("bigram", (int(self.bigram_spec[0]) + 1, self.width)))
+        if self.max_positions is not None:
+            out.append(TensorDecl("positions", (int(self.max_positions), self.width)))
+        return out
+
+    def state_bytes(self) -> int:
+        return 4 if self.bigram_spec is not None else 0
+
+    def bind(self, tensors, dtype, device):
+        self.table = tensors["table"]
+        self.bigram = tensors.get("bigram")
+        self.positions = tensors.get("positions")
+        ops.declare_weights(self.table, self.bigram, self.positions)
+
+    def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
+        x = ctx.scratch("residual", (token_ids.shape[0], self.width), torch.float32)
+        state = ctx.state(self.state_binding) if self.state_binding is not None else None
+        buckets, mul_prev, mul_cur = self.bigram_spec if self.bigram_spec is not None else (0, 0, 0)
+        ops.hashed_embedding(self.table, self.bigram, self.positions, token_ids, ctx, state, x, self.scale,
+                             int(buckets), int(mul_prev), int(mul_cur),
+                             getattr(ctx, "device_tokens", None))
+        return x
+
+
 class LMHead(Head):
     def __init__(self, vocab_size: int, width: int, tied: bool):
         self.vocab_size = vocab_size
@@ -88,4 +131,5 @@ class LMHead(Head):
 
 EMBEDDINGS.register("token", lambda spec, vocab, width: TokenEmbedding(vocab, width))
 EMBEDDINGS.register("token_normed_streams", NormedStreamsEmbedding)
+EMBEDDINGS.register("token_hashed_positions", HashedPositionEmbedding)
 HEADS.register("linear", lambda spec, vocab, width, tied: LMHead(vocab, width, tied))

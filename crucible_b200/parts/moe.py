@@ -1,0 +1,104 @@
+"""Feed-forwards of this family: a dense one with a chosen activation, and a mixture of
+experts.
+
+`dense_act`: x += act(h Wup^T) Wdown^T; the activation is an option of the spec (relu2:
+the square of ReLU; gelu_tanh; silu; tanh).
+
+`moe`: `experts` gated feed-forwards Wd_e (silu(Wg_e h) * (Wu_e h)) without biases, of
+which a token uses the `top` with the largest router logits z = h Wr^T (float32; the lower
+index on ties), weighted by the softmax over those `top` logits alone; an optional shared
+expert of the same form runs for every token and is added.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.model_config import FeedForwardSpec
+from ..ops import moe as kernels
+from .base import FEED_FORWARDS, FeedForward, TensorDecl
+from .swiglu import SwiGLU
+
+
+class ActivatedFeedForward(FeedForward):
+    def __init__(self, spec: FeedForwardSpec):
+        self.spec = spec
+        self.kind = str(spec.option("activation", "relu2"))
+        if self.kind not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_act: unknown activation {self.kind!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.up = self.down = None
+
+    def tensors(self):
+        d, f = self.spec.width, self.spec.intermediate
+        return [TensorDecl("up", (f, d)), TensorDecl("down", (d, f))]
+
+    def bind(self, tensors, dtype, device):
+        self.up, self.down = tensors["up"], tensors["down"]
+        ops.declare_weights(self.up, self.down)
+        self.dtype = dtype
+
+    def forward(self, ctx, h, residual):
+        z = ctx.scratch("ffn.z", (h.shape[0], self.spec.intermediate), self.dtype)
+        ops.linear(h, self.up, z)
+        ops.activation(self.kind, z, z)
+        ops.linear(z, self.down, residual, accumulate=True, closes=ctx)
+
+
+class MixtureOfExperts(FeedForward):
+    def __init__(self, spec: FeedForwardSpec):
+        self.spec = spec
+        self.n = int(spec.option("experts", 0))
+        self.top = int(spec.option("top", 0))
+        self.ff = int(spec.intermediate)
+        shared = spec.option("shared_intermediate")
+        if self.n <= 0 or not 0 < self.top <= self.n or self.ff <= 0:
+            raise ValueError("moe: experts, top (at most experts) and the experts' ff must be positive")
+        if self.n > 256 or self.top > 32:
+            raise ValueError("moe: up to 256 experts, of which a token uses up to 32")
+        self.shared = (SwiGLU(FeedForwardSpec(kind="swiglu", width=spec.width, intermediate=int(shared)))
+                       if shared else None)
+
+    def tensors(self):
+        d, f = self.spec.width, self.ff
+        out = [TensorDecl("router", (self.n, d))]
+        for e in range(self.n):
+            out += [TensorDecl(f"e{e}.gate", (f, d)), TensorDecl(f"e{e}.up", (f, d)),
+                    TensorDecl(f"e{e}.down", (d, f))]
+        if self.shared is not None:
+            out += [TensorDecl(f"shared.{t.name}", t.shape, t.role) for t in self.shared.tensors()]
+        return out
+
+    def bind(self, tensors, dtype, device):
+        self.dtype = dtype
+        self.router = tensors["router"]
+        self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], 0)
+                                    for e in range(self.n)], 0).contiguous()          # [E, 2F, d]
+        self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.n)], 0).contiguous()   # [E, d, F]
+        ops.declare_weights(self.router, self.gate_up, self.down)
+        self.count = torch.zeros(self.n, dtype=torch.int32, device=device)     # zero between steps
+        if self.shared is not None:
+            self.shared.bind({k[len("shared."):]: v for k, v in tensors.items() if k.startswith("shared.")},
+                             dtype, device)
+
+    def forward(self, ctx, h, residual):
+        t, d, top, n, f = h.shape[0], self.spec.width, self.top, self.n, self.ff
+        logits = ctx.scratch("moe.logits", (t, n), torch.float32)
+        ops.linear(h, self.router, logits)
+        tiles = kernels.max_tiles(t, top, n)
+        idx = ctx.scratch("moe.idx", (t * top,), torch.int32)
+        place = ctx.scratch("moe.place", (t * top,), torch.int32)
+        order = ctx.scratch("moe.order", (t * top,), torch.int32)
+        weight = ctx.scratch("moe.weight", (t * top,), torch.float32)
+        plan = ctx.scratch("moe.plan", (kernels.plan_ints(n, tiles),), torch.int32)
+        kernels.route(logits, top, idx, weight, place, self.count, plan, tiles, order)
+        act = ctx.scratch("moe.act", (t * top, f), self.dtype)
+        kernels.expert_tiles(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act)
+        pair_out = ctx.scratch("moe.pair_out", (t * top, d), torch.float32)
+        kernels.expert_tiles(False, act, self.down, d, plan, n, tiles, order, top, weight, pair_out)
+        kernels.combine(pair_out, top, residual)
+        if self.shared is not None:
+            self.shared.forward(ctx, h, residual)
+
+
+FEED_FORWARDS.register("dense_act", ActivatedFeedForward)
+FEED_FORWARDS.register("moe", MixtureOfExperts)

@@ -15,6 +15,21 @@ log gates i = cap * tanh((h Wi^T + bi) / cap), f = logsigmoid(cap * tanh((h Wf^T
 with m (from 0):  m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;
 n likewise with k alone;  o = S^T q / (max(|n . q|, exp(-m')) + 1e-6).
 o / rms(o) per head, times norm [H * E], times sigmoid(h Wg^T), goes through Wo.
+
+`wkv` (time mixing with a decay per key channel): with h' the row of the token before
+(zeros at a sequence's start; the last row seen is state), each of r, k, v, g, w reads its
+own mix  h + (h' - h) * mu_s.  r, k, v = W_s mix_s [H, D]; gate = silu(Wg mix_g); decay
+w = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0)) per head and key channel (W_w1 has as many rows
+as the checkpoint gives it).  Per head:
+    o = (S + diag(u) k v^T)^T r;   S <- diag(w) S + k v^T.
+o / rms(o) per head, times norm [H * D], times the gate, goes through Wo.
+
+`mamba2` (state space): h W_in^T = [z: H*P | x: H*P | B: G*N | C: G*N | dt: H]; x, B, C pass
+a short causal convolution per channel with bias (its last taps - 1 inputs are state) and
+SiLU; dt = softplus(dt + dt_bias).  Per head (head i uses group i // (H / G)):
+    S <- exp(-exp(A_log) dt) S + dt B x^T;   y = S^T C + D x.
+y * silu(z), then unit rms in `norm_groups` equal parts of the row, times norm [H * P], goes
+through Wo.
 """
 from __future__ import annotations
 
@@ -22,7 +37,8 @@ import torch
 
 from ..config.model_config import MixerSpec
 from ..ops import recurrent as kernels
-from .base import MIXERS, TensorDecl
+from .. import ops
+from .base import MIXERS, Mixer, TensorDecl
 from .branch import BranchMixer
 
 
@@ -136,5 +152,133 @@ class MLSTM(BranchMixer):
                                self.eps, out_scale)
 
 
+class WKVMixer(Mixer):
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, spec: MixerSpec):
+        s = self.spec = spec
+        self.H, self.D = s.n_heads, s.head_dim
+        self.rank = int(s.option("decay_rank", 16))
+        self.eps = float(s.option("norm_eps", 1e-6))
+        if self.H <= 0 or self.D <= 0 or self.rank <= 0:
+            raise ValueError("wkv: heads, dim and the decay's rank must be positive")
+        if self.D > 256:
+            raise ValueError("wkv: key size up to 256")
+        self.s_bytes = _round16(4 * self.H * self.D * self.D)
+        self.prev_bytes = _round16(4 * s.width)
+
+    def tensors(self):
+        d, HD = self.spec.width, self.H * self.D
+        out = [TensorDecl(f"mu.{m}", (d,), role="vector", init=("uniform", 0.0, 1.0)) for m in self.MIXES]
+        out += [TensorDecl(m, (HD, d)) for m in ("r", "k", "v", "g")]
+        out += [TensorDecl("w1", (self.rank, d), free_dims=(0,)),
+                TensorDecl("w2", (HD, self.rank), free_dims=(1,)),
+                TensorDecl("w0", (HD,), role="vector", init=("uniform", -3.0, 0.0)),
+                TensorDecl("u", (self.H, self.D), role="vector", init=("normal", 0.0, 0.5)),
+                TensorDecl("norm", (HD,), role="vector"), TensorDecl("o", (d, HD))]
+        return out
+
+    def bind(self, tensors, dtype, device):
+        self.mu = torch.stack([tensors[f"mu.{m}"] for m in self.MIXES], 0).contiguous()
+        self.w_proj = [tensors[m] for m in ("r", "k", "v", "g")]
+        self.w1, self.w2, self.w_out = tensors["w1"], tensors["w2"], tensors["o"]
+        if self.w1.shape[0] != self.w2.shape[1]:
+            raise ValueError(f"wkv: the decay's two matrices disagree on its rank "
+                             f"({self.w1.shape[0]} and {self.w2.shape[1]})")
+        self.rank = int(self.w1.shape[0])
+        self.w0, self.u, self.gain = tensors["w0"], tensors["u"].contiguous(), tensors["norm"]
+        self.dtype = dtype
+        ops.declare_weights(*self.w_proj, self.w1, self.w2, self.w_out)
+
+    def state_bytes(self) -> int:
+        return self.s_bytes + self.prev_bytes
+
+    def forward(self, ctx, h, residual, binding):
+        t, d, H, D = h.shape[0], self.spec.width, self.H, self.D
+        HD = H * D
+        state = ctx.state(binding)
+        mixes = ctx.scratch("wkv.mixes", (len(self.MIXES), t, d), self.dtype)
+        kernels.shift_mix(h, self.mu, ctx, state, self.s_bytes, mixes)
+        rkvg = ctx.scratch("wkv.rkvg", (4, t, HD), self.dtype)
+        for i, w in enumerate(self.w_proj):
+            ops.linear(mixes[i], w, rkvg[i])
+        low = ctx.scratch("wkv.low", (t, self.rank), torch.float32)
+        ops.linear(mixes[4], self.w1, low)
+        low_t = ctx.scratch("wkv.low_t", (t, self.rank), self.dtype)
+        ops.activation("tanh", low, low_t)
+        logit = ctx.scratch("wkv.logit", (t, HD), torch.float32)
+        ops.linear(low_t, self.w2, logit)
+        qkv = ctx.scratch("wkv.qkv", (t, 4 * HD), torch.float32)
+        kernels.wkv_prepare(rkvg, logit, self.w0, qkv, HD)
+        o = ctx.scratch("wkv.o", (t, HD), torch.float32)
+        kernels.matrix_memory(kernels.WKV, qkv, 0, HD, 2 * HD, None, None, ctx, state, 0, 0, 0, o,
+                              H, H, D, D, w_off=3 * HD, per_head=self.u)
+        act = ctx.scratch("wkv.act", (t, HD), self.dtype)
+        kernels.head_norm_gate(o, self.gain, True, rkvg[3], act, kernels.GATE_SILU, H, D, self.eps, 1.0)
+        ops.linear(act, self.w_out, residual, accumulate=True, closes=ctx)
+
+
+class StateSpaceMixer(BranchMixer):
+    def __init__(self, spec: MixerSpec):
+        s = self.spec = spec
+        self.H, self.G, self.N = s.n_heads, s.n_kv_heads, s.head_dim
+        self.P = int(s.option("value_dim", s.head_dim))
+        self.taps = int(s.option("conv_taps", 4))
+        self.parts = int(s.option("norm_groups", 1))
+        self.eps = float(s.option("norm_eps", 1e-6))
+        self.inner = self.H * self.P
+        if self.H <= 0 or self.G <= 0 or self.H % self.G or self.N <= 0 or self.P <= 0 or self.taps < 1:
+            raise ValueError("mamba2: heads must be a multiple of groups; sizes positive")
+        if self.parts <= 0 or self.inner % self.parts:
+            raise ValueError("mamba2: norm_groups must divide heads * vdim")
+        if self.N > 256:
+            raise ValueError("mamba2: state size up to 256")
+        self.C = self.inner + 2 * self.G * self.N           # channels under the convolution
+        self.s_bytes = _round16(4 * self.H * self.N * self.P)
+        self.tail_bytes = 4 * (self.taps - 1) * self.C
+
+    def tensors(self):
+        d, H = self.spec.width, self.H
+        return [TensorDecl("in", (self.inner + self.C + H, d)),
+                TensorDecl("conv", (self.C, self.taps), role="vector", init=("uniform", -0.5, 0.5)),
+                TensorDecl("conv.b", (self.C,), role="vector", init=("uniform", -0.2, 0.2)),
+                TensorDecl("dt_bias", (H,), role="vector", init=("uniform", -2.0, 1.0)),
+                TensorDecl("A_log", (H,), role="vector", init=("uniform", -1.0, 1.0)),
+                TensorDecl("D", (H,), role="vector", init=("normal", 1.0, 0.3)),
+                TensorDecl("norm", (self.inner,), role="vector"), TensorDecl("o", (d, self.inner))]
+
+    def bind(self, tensors, dtype, device):
+        n = self.inner + self.C
+        self.w_in = tensors["in"][:n].contiguous()
+        self.w_gates = tensors["in"][n:].contiguous()
+        self.w_out = tensors["o"]
+        self.conv_w, self.conv_b = tensors["conv"].contiguous(), tensors["conv.b"]
+        self.a_log, self.dt_bias, self.skip = tensors["A_log"], tensors["dt_bias"], tensors["D"]
+        self.gain = tensors["norm"]
+        self.dtype = dtype
+        self._declare()
+
+    def state_bytes(self) -> int:
+        return self.s_bytes + self.tail_bytes
+
+    def run_branch(self, ctx, proj, gates, act, out_scale, binding):
+        if out_scale != 1.0:
+            raise ValueError("mamba2: a branch scale other than 1 is not supported")
+        t, H, G, N, P, C, inner = proj.shape[0], self.H, self.G, self.N, self.P, self.C, self.inner
+        state = ctx.state(binding)
+        xbc = ctx.scratch("ssd.xbc", (t, C), torch.float32)
+        decay = ctx.scratch("ssd.decay", (t, H), torch.float32)
+        step = ctx.scratch("ssd.step", (t, H), torch.float32)
+        y = ctx.scratch("ssd.y", (t, inner), torch.float32)
+        kernels.ssd_prepare(proj, inner, self.conv_w, self.conv_b, self.taps, gates, self.a_log,
+                            self.dt_bias, ctx, state, self.s_bytes, xbc, decay, step, H, C)
+        kernels.conv_tail_update(proj[:, inner:inner + C], self.taps, C, ctx, state, self.s_bytes)
+        kernels.matrix_memory(kernels.SSD, xbc, inner + G * N, inner, 0, decay, step, ctx, state, 0, 0, 0,
+                              y, H, G, N, P, per_head=self.skip)
+        kernels.gate_group_norm(y, proj[:, :inner], self.gain, act, self.parts, self.eps)
+
+
 MIXERS.register("gated_delta", GatedDeltaRule)
+MIXERS.register("wkv", WKVMixer)
+MIXERS.register("mamba2", StateSpaceMixer)
 MIXERS.register("mlstm", MLSTM)

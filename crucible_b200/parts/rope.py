@@ -75,3 +75,50 @@ class InterleavedRotary(PositionEncoding):
 
 
 POSITIONS.register("rope_interleaved", InterleavedRotary)
+
+
+class YarnRotary(PositionEncoding):
+    """Half-split pairs (feature i with i + rotary_dim / 2) whose frequencies are stretched for
+    contexts beyond the one the model was trained at.  With f_i = theta^(-2i / n):
+        dim(t) = n ln(original / (2 pi t)) / (2 ln theta),
+        lo = max(floor(dim(fast)), 0),  hi = min(ceil(dim(slow)), n - 1),
+        ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+        frequency_i = f_i / factor * ramp_i + f_i * (1 - ramp_i),
+    and cos and sin are multiplied by 0.1 ln(factor) + 1 (`magnitude()`).  Without the options
+    `factor`, `original`, `fast`, `slow` (the spec's `extra`) the frequencies are the base's and the
+    magnitude is 1.  The angle is a float32 product of position and frequency taken in the kernel."""
+
+    def __init__(self, spec: PositionSpec, scaling=None):
+        if spec.rotary_dim % 2 != 0 or spec.rotary_dim < 0:
+            raise ValueError(f"rotary_dim must be even and not negative, got {spec.rotary_dim}")
+        self.spec = spec
+        self.scaling = dict(scaling) if scaling else None
+        self.freq = None
+
+    def _frequencies(self) -> torch.Tensor:
+        import math
+        n, base = self.spec.rotary_dim, float(self.spec.theta)
+        i = torch.arange(n // 2, dtype=torch.float64)
+        f = base ** (-2.0 * i / n)
+        sc = self.scaling
+        if sc:
+            def dim_of(turns):
+                return n * math.log(sc["original"] / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+            lo = max(math.floor(dim_of(sc["fast"])), 0)
+            hi = min(math.ceil(dim_of(sc["slow"])), n - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / sc["factor"] * ramp + f * (1.0 - ramp)
+        return f.to(torch.float32)
+
+    def magnitude(self) -> float:
+        import math
+        return 0.1 * math.log(self.scaling["factor"]) + 1.0 if self.scaling else 1.0
+
+    def bind(self, tensors, dtype, device):
+        self.freq = self._frequencies().to(device) if self.spec.rotary_dim else None
+
+    def frequencies(self):
+        return self.freq, self.spec.rotary_dim
+
+
+POSITIONS.register("rope_yarn", lambda spec: YarnRotary(spec, spec.scaling))

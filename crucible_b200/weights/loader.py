@@ -47,6 +47,14 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def _shape_fits(stored, decl) -> bool:
+    """Equal shapes, but for the axes whose size the declaration leaves to the checkpoint."""
+    if len(stored) != len(decl.shape):
+        return False
+    return all(int(a) == int(b) or (i in decl.free_dims and int(a) > 0)
+               for i, (a, b) in enumerate(zip(stored, decl.shape)))
+
+
 def load_weights(model, model_dir: str, dtype: torch.dtype, device) -> None:
     """Reads model.safetensors of `model_dir` into `model` (a DecoderModel)."""
     if dtype not in (torch.bfloat16, torch.float32):
@@ -66,7 +74,7 @@ def load_weights(model, model_dir: str, dtype: torch.dtype, device) -> None:
                     missing.append(r.checkpoint_name)
                 continue
             e = f.entries[r.checkpoint_name]
-            if tuple(e.shape) != tuple(r.decl.shape):
+            if not _shape_fits(e.shape, r.decl):
                 wrong_shape.append((r.checkpoint_name, e.shape, r.decl.shape))
             stored = {"F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16}.get(e.dtype)
             if r.decl.role == "int_table":
