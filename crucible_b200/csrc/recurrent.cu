@@ -332,25 +332,25 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
                     }
 #pragma unroll
                     for (int i = 0; i < P; ++i) {
-                        const float kv = kk[i] * v;
+                        const float kv = __fmul_rn(kk[i], v);
                         oc[i & 3] = fmaf(fmaf(n[i], kv, s[i]), qq[i], oc[i & 3]);
                         s[i] = fmaf(ww[i], s[i], kv);
                     }
                 } else {
-                    const float a = s0[tt], dv = s1[tt] * v;
+                    const float a = s0[tt], dv = __fmul_rn(s1[tt], v);
 #pragma unroll
                     for (int i = 0; i < P; ++i) {
-                        s[i] = fmaf(kk[i], dv, a * s[i]);
+                        s[i] = fmaf(kk[i], dv, __fmul_rn(a, s[i]));
                         oc[i & 3] = fmaf(s[i], qq[i], oc[i & 3]);
                     }
                 }
                 if (pending) {
 #pragma unroll
                     for (int x = 1; x < LANES; x <<= 1) p_o += __shfl_xor_sync(0xffffffffu, p_o, x);
-                    if (live && part == 0) out[p_at] = p_o + p_n;
+                    if (live && part == 0) out[p_at] = __fadd_rn(p_o, p_n);
                 }
                 p_o = (oc[0] + oc[1]) + (oc[2] + oc[3]);
-                p_n = skip * v;
+                p_n = __fmul_rn(skip, v);      // never fused with the sum: every token rounds alike
                 p_at = out_at;
                 pending = true;
             } else {
@@ -393,7 +393,7 @@ __global__ void __launch_bounds__(THREADS) matrix_memory_kernel(
     } else if ((RULE == RULE_WKV || RULE == RULE_SSD) && pending) {
 #pragma unroll
         for (int x = 1; x < LANES; x <<= 1) p_o += __shfl_xor_sync(0xffffffffu, p_o, x);
-        if (live && part == 0) out[p_at] = p_o + p_n;
+        if (live && part == 0) out[p_at] = __fadd_rn(p_o, p_n);
     } else if (pending) {
 #pragma unroll
         for (int x = 1; x < LANES; x <<= 1) {
