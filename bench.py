@@ -621,25 +621,28 @@ def run_profile_case(args):
 
 
 def run_design_comparison(args):
-    """`--compare vuvosun`: prefill and decode throughput of the Vuvosun design at a few sizes
-    of a real model's proportions (random weights), beside the dense Llama-style decoder at
-    equal width, layers, heads, feed-forward width and vocabulary; and, from one eager
-    prompt step and one eager decode step each, the device time of every kind of launch."""
+    """`--compare vuvosun` / `--compare futepel`: prefill and decode throughput of that design at
+    a few sizes of a real model's proportions (random weights), beside the dense Llama-style
+    decoder (and, for futepel, beside Vuvosun, the nearest design with recurrent mixers) at
+    equal width, layers, heads, feed-forward width and vocabulary; and, from one eager prompt
+    step and one eager decode step each, the device time of every kind of launch."""
     import torch
     from crucible_b200 import ops
     from crucible_b200.config import parse_config
-    from crucible_b200.config.presets import COMPARISON_SIZES, _llama, vuvosun
+    from crucible_b200.config.presets import COMPARISON_SIZES, _llama, futepel, vuvosun
     from crucible_b200.engine import Engine, EngineOptions, StepEntry
     from crucible_b200.weights import write_random_model
     peaks = read_peaks()
     rng = random.Random(1)
     t_prefill, ctx_len, batch, layers = 2048, args.context, args.batch, args.layers or 4
-    out = {"compare": "vuvosun", "dtype": "bf16", "data": "synthetic", "layers": layers,
+    out = {"compare": args.compare, "dtype": "bf16", "data": "synthetic", "layers": layers,
            "prefill_tokens": t_prefill, "decode_batch": batch, "decode_context": ctx_len,
            "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops")}, "sizes": {}}
     for label, (width, heads, kv, hd, ff, vocab) in COMPARISON_SIZES.items():
         raws = {"vuvosun": vuvosun(width, heads, kv, hd, ff, vocab, layers=layers),
                 "llama": _llama(vocab, layers, heads, kv, width, hd, ff, 8192, 10000.0, 1e-5, True)}
+        if args.compare == "futepel":
+            raws = dict(futepel=futepel(width, heads, kv, hd, ff, vocab, layers=layers), **raws)
         row = {}
         for design, raw in raws.items():
             pages = (batch + 1) * (-(-(ctx_len + args.steps + args.warmup + 64) // 16)) + 256
@@ -698,14 +701,14 @@ def main():
     p.add_argument("--impl", default="ours", choices=["ours", "reference", "cpu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
-    p.add_argument("--shape", default="120m", choices=sorted(SHAPE_LABEL) + ["vuvosun-w1024", "vuvosun-w2048"],
-                   help="a named shape; the default is the benchmark's (the vuvosun shapes: with "
-                        "--profile-case only; their numbers come from --compare vuvosun)")
+    p.add_argument("--shape", default="120m", choices=sorted(SHAPE_LABEL) + ["vuvosun-w1024", "vuvosun-w2048", "futepel-w1024", "futepel-w2048"],
+                   help="a named shape; the default is the benchmark's (the vuvosun and futepel shapes: "
+                        "with --profile-case only; their numbers come from --compare)")
     p.add_argument("--layers", type=int, default=0,
                    help="fewer layers than the shape has (both numbers are reported)")
     p.add_argument("--profile-case", default=None, choices=["prefill", "decode"],
                    help="run a small eager workload for a profiler instead of the benchmark")
-    p.add_argument("--compare", default=None, choices=["vuvosun"],
+    p.add_argument("--compare", default=None, choices=["vuvosun", "futepel"],
                    help="instead of the benchmark: this design beside the dense decoder at equal sizes")
     args = p.parse_args()
     if args.compare:
@@ -716,7 +719,7 @@ def main():
     if args.profile_case:
         return run_profile_case(args)
     if args.shape not in SHAPE_LABEL:
-        print(f"bench.py: --shape {args.shape} runs with --profile-case; use --compare vuvosun for its numbers")
+        print(f"bench.py: --shape {args.shape} runs with --profile-case; use --compare for its numbers")
         return 2
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

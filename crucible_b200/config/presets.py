@@ -68,3 +68,34 @@ COMPARISON_SIZES = {"w1024": (1024, 8, 2, 128, 2816, 32000), "w2048": (2048, 16,
 
 SHAPES["vuvosun-w1024"] = vuvosun(*COMPARISON_SIZES["w1024"])
 SHAPES["vuvosun-w2048"] = vuvosun(*COMPARISON_SIZES["w2048"])
+
+
+def futepel(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int,
+            layers: int = 4, experts: int = 8, top: int = 2, max_positions: int = 8192) -> dict:
+    """A Futepel config.json of a real model's proportions: `layers` layers that take turns as
+    state space + dense feed-forward, wkv + experts, wkv + dense, latent attention + experts;
+    every mixer `heads * head_dim` wide (the wkv heads are 64 wide), the latent's cached row
+    256 features (192 of latent, 64 rotated), `experts` experts of half the dense width of which
+    a token uses `top`, beside a shared one of that width."""
+    inner = heads * head_dim
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // 2},
+           "shared": {"ff": ff // 2}}
+    mamba = {"type": "mamba2", "mlp": dense,
+             "mixer": {"heads": heads, "vdim": head_dim, "state": 128, "groups": max(1, kv_heads // 2),
+                       "conv": 4, "norm_groups": 1}}
+    wkv = {"type": "wkv", "mixer": {"heads": inner // 64, "dim": 64, "decay_rank": 64}}
+    latent = {"type": "latent_attention", "mlp": moe,
+              "mixer": {"heads": heads, "dim": head_dim, "rot_dim": 64, "vdim": head_dim, "kv_rank": 192,
+                        "scale": (head_dim + 64) ** -0.5,
+                        "rot": {"base": 10000.0, "dims": 64,
+                                "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+    cycle = [mamba, dict(wkv, mlp=moe), dict(wkv, mlp=dense), latent]
+    return {"architecture": "Futepel", "vocab": vocab, "width": width, "max_positions": max_positions,
+            "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 1000003,
+                                                                       "mul_cur": 31}},
+            "layers": [cycle[i % 4] for i in range(layers)]}
+
+
+SHAPES["futepel-w1024"] = futepel(*COMPARISON_SIZES["w1024"])
+SHAPES["futepel-w2048"] = futepel(*COMPARISON_SIZES["w2048"])

@@ -15,9 +15,9 @@
 
 namespace {
 
-constexpr int MAX_PER_LANE = 8;   // head_dim <= 256
-
-template <typename T>
+// a lane holds MAX_PER_LANE features of its row: 8 for heads up to 256 features, 32 for the rows
+// of up to 1024 that a cached latent shared by all heads can have
+template <typename T, int MAX_PER_LANE>
 __global__ void attention_generic_kernel(
     const T* __restrict__ qkv, int qkv_stride, T* __restrict__ out, int out_stride,
     const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -86,21 +86,21 @@ CB_EXPORT int cb_attention_generic(const void* qkv, int qkv_stride, void* out, i
                                    int n_heads, int n_kv_heads, int head_dim, int page_tokens,
                                    float scale, int window, void* stream) {
     if (n_rows <= 0) return 0;
-    if (head_dim > 32 * MAX_PER_LANE || n_heads % n_kv_heads != 0) return CB_ERR_UNSUPPORTED;
+    if (head_dim > 1024 || n_heads % n_kv_heads != 0) return CB_ERR_UNSUPPORTED;
     const int warps = 4;
     const long units = (long)n_rows * n_heads;
     const int blocks = (int)((units + warps - 1) / warps);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == CB_F32)
-        cb_launch(attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), 0, s, 
-            (const float*)qkv, qkv_stride, (float*)out, out_stride, (const float*)k_cache,
-            (const float*)v_cache, positions, row_request, block_table, table_stride, n_rows,
-            n_heads, n_kv_heads, head_dim, page_tokens, scale, window);
-    else
-        cb_launch(attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, s, 
-            (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)out, out_stride,
-            (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, row_request,
-            block_table, table_stride, n_rows, n_heads, n_kv_heads, head_dim, page_tokens, scale,
-            window);
+#define CB_GENERIC(TT, PER)                                                                            \
+    cb_launch(attention_generic_kernel<TT, PER>, dim3(blocks), dim3(warps * 32), 0, s, (const TT*)qkv,  \
+              qkv_stride, (TT*)out, out_stride, (const TT*)k_cache, (const TT*)v_cache, positions,      \
+              row_request, block_table, table_stride, n_rows, n_heads, n_kv_heads, head_dim,            \
+              page_tokens, scale, window)
+    if (dtype == CB_F32) {
+        if (head_dim <= 256) CB_GENERIC(float, 8); else CB_GENERIC(float, 32);
+    } else {
+        if (head_dim <= 256) CB_GENERIC(__nv_bfloat16, 8); else CB_GENERIC(__nv_bfloat16, 32);
+    }
+#undef CB_GENERIC
     return cb_last_error();
 }

@@ -84,7 +84,59 @@ __global__ void head_gate_kernel(T* __restrict__ x, int x_stride, const float* _
     }
 }
 
+// Per-head products of a step of few rows: out[t][h][n] = sum_k a[t][h][k] * w[h][n][k].
+// One warp per (head, output feature): its lanes share K, the weight row is read once and meets
+// every row of the step (up to ROWS at a time).  a: rows with a_stride, head h at h * a_head;
+// out likewise.  fp32 sums.
+template <typename T, int ROWS>
+__global__ void heads_linear_small_kernel(const T* __restrict__ a, int a_stride, int a_head,
+                                          const T* __restrict__ w, T* __restrict__ out, int out_stride,
+                                          int out_head, int n_rows, int n_heads, int N, int K) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= n_heads * N) return;
+    const int lane = threadIdx.x & 31;
+    const int h = unit / N, n = unit - h * N;
+    const T* wr = w + ((size_t)h * N + n) * K;
+    for (int t0 = 0; t0 < n_rows; t0 += ROWS) {
+        float acc[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = cb_to_float(wr[k]);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (t0 + r < n_rows)
+                    acc[r] = fmaf(cb_to_float(a[(size_t)(t0 + r) * a_stride + (size_t)h * a_head + k]), wv, acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const float v = cb_warp_sum(acc[r]);
+            if (lane == 0 && t0 + r < n_rows)
+                out[(size_t)(t0 + r) * out_stride + (size_t)h * out_head + n] = cb_from_float<T>(v);
+        }
+    }
+}
+
 }  // namespace
+
+CB_EXPORT int cb_heads_linear_small(const void* a, int a_stride, int a_head, const void* w, void* out,
+                                    int out_stride, int out_head, int dtype, int n_rows, int n_heads,
+                                    int N, int K, void* stream) {
+    if (n_rows <= 0 || n_heads <= 0 || N <= 0) return 0;
+    const int warps = 4;
+    const dim3 grid((unsigned)(((long)n_heads * N + warps - 1) / warps)), block(warps * 32);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(heads_linear_small_kernel<float, 8>, grid, block, 0, s, (const float*)a, a_stride, a_head,
+                  (const float*)w, (float*)out, out_stride, out_head, n_rows, n_heads, N, K);
+    else
+        cb_launch(heads_linear_small_kernel<__nv_bfloat16, 8>, grid, block, 0, s, (const __nv_bfloat16*)a,
+                  a_stride, a_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, out_head, n_rows,
+                  n_heads, N, K);
+    return cb_last_error();
+}
 
 CB_EXPORT int cb_latent_prepare(const void* dkv, int dkv_stride, const void* q, int q_stride, void* qx,
                                 int qx_stride, int dtype, const float* gain, const float* freq,

@@ -178,6 +178,119 @@ __global__ void __launch_bounds__(THREADS) moe_tile_kernel(
     }
 }
 
+// The same two products for steps of few rows (decoded tokens): the experts' weights are what
+// moves, so each weight row is read once, by one warp whose lanes share K in 16-byte pieces, and
+// meets every row of its tile (ROWS at a time).  A block owns a tile and a run of output features.
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+    typedef uint4 Raw;
+    static __device__ __forceinline__ Raw fetch(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+    static __device__ __forceinline__ void put(__nv_bfloat16* p, const Raw& raw) { *reinterpret_cast<uint4*>(p) = raw; }
+    static __device__ __forceinline__ void unpack(const Raw& raw, float* v) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+};
+template <> struct Vec8<float> {
+    struct Raw { float4 a, b; };
+    static __device__ __forceinline__ Raw fetch(const float* p) {
+        Raw r;
+        r.a = *reinterpret_cast<const float4*>(p);
+        r.b = *reinterpret_cast<const float4*>(p + 4);
+        return r;
+    }
+    static __device__ __forceinline__ void put(float* p, const Raw& r) {
+        *reinterpret_cast<float4*>(p) = r.a;
+        *reinterpret_cast<float4*>(p + 4) = r.b;
+    }
+    static __device__ __forceinline__ void unpack(const Raw& r, float* v) {
+        v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+    }
+};
+
+extern __shared__ __align__(16) unsigned char moe_rows_staged[];
+
+template <typename T, bool GATED, int ROWS>
+__global__ void __launch_bounds__(256, 3) moe_rows_small_kernel(
+    const T* __restrict__ a, int a_stride, const T* __restrict__ w, long expert_stride, int N, int K,
+    const int* __restrict__ plan, int E, int max_tiles, const int* __restrict__ sorted_pair, int top,
+    const float* __restrict__ weight, void* __restrict__ out_, int out_stride, int per_block) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= plan[0]) return;
+    const int* tile_expert = plan + 2 + E;
+    const int e = tile_expert[tile], start = tile_expert[max_tiles + tile], rows = tile_expert[2 * max_tiles + tile];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const T* we = w + (size_t)e * expert_stride;
+    const int n_end = min(N, (int)(blockIdx.y + 1) * per_block);
+    T* staged = reinterpret_cast<T*>(moe_rows_staged);       // ROWS rows of K: this pass's rows
+    for (int r0 = 0; r0 < rows; r0 += ROWS) {
+        __syncthreads();
+        for (int i = threadIdx.x * 8; i < ROWS * K; i += blockDim.x * 8) {
+            const int r = i / K, k = i - r * K;
+            const int s = start + min(r0 + r, rows - 1);
+            Vec8<T>::put(staged + i, Vec8<T>::fetch(a + (size_t)(GATED ? sorted_pair[s] / top : s) * a_stride + k));
+        }
+        __syncthreads();
+        for (int n = blockIdx.y * per_block + warp; n < n_end; n += n_warps) {
+            const T* w0 = we + (size_t)n * K;
+            const T* w1 = we + (size_t)(N + n) * K;          // the up row (GATED)
+            float acc0[ROWS], acc1[ROWS];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) acc0[r] = acc1[r] = 0.f;
+            // four pieces of a weight row are asked for before the first is used: a warp then has
+            // 2 to 4 KB on its way, a block of eight warps what an SM needs to stream
+            constexpr int AHEAD = 4;
+            for (int k = lane * 8; k < K; k += 256 * AHEAD) {
+                typename Vec8<T>::Raw raw0[AHEAD], raw1[AHEAD];
+#pragma unroll
+                for (int u = 0; u < AHEAD; ++u) {
+                    const int kk = k + u * 256;
+                    if (kk < K) {
+                        raw0[u] = Vec8<T>::fetch(w0 + kk);
+                        if (GATED) raw1[u] = Vec8<T>::fetch(w1 + kk);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < AHEAD; ++u) {
+                    const int kk = k + u * 256;
+                    if (kk >= K) break;
+                    float wv0[8], wv1[8], av[8];
+                    Vec8<T>::unpack(raw0[u], wv0);
+                    if (GATED) Vec8<T>::unpack(raw1[u], wv1);
+#pragma unroll
+                    for (int r = 0; r < ROWS; ++r) {
+                        if (r0 + r >= rows) break;
+                        Vec8<T>::unpack(Vec8<T>::fetch(staged + r * K + kk), av);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            acc0[r] = fmaf(av[i], wv0[i], acc0[r]);
+                            if (GATED) acc1[r] = fmaf(av[i], wv1[i], acc1[r]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (r0 + r >= rows) break;
+                const float g = cb_warp_sum(acc0[r]);
+                const float u = GATED ? cb_warp_sum(acc1[r]) : 0.f;
+                if (lane == 0) {
+                    const int s = start + r0 + r;
+                    if (GATED) {
+                        reinterpret_cast<T*>(out_)[(size_t)s * out_stride + n] = cb_from_float<T>(silu_f(g) * u);
+                    } else {
+                        const int p = sorted_pair[s];
+                        reinterpret_cast<float*>(out_)[(size_t)p * out_stride + n] = weight[p] * g;
+                    }
+                }
+            }
+        }
+    }
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ pair_out, int top, float* __restrict__ residual,
                                    int width) {
     cb_pdl_trigger();
@@ -240,6 +353,42 @@ CB_EXPORT int cb_moe_tiles(int gated, const void* a, int a_stride, const void* w
 #define CB_MOE(TT, GG)                                                                             \
     cb_launch(moe_tile_kernel<TT, GG>, grid, block, 0, s, (const TT*)a, a_stride, (const TT*)w,    \
               expert_stride, N, K, plan, E, max_tiles, sorted_pair, top, weight, out, out_stride)
+    if (dtype == CB_F32) { if (gated) CB_MOE(float, true); else CB_MOE(float, false); }
+    else { if (gated) CB_MOE(__nv_bfloat16, true); else CB_MOE(__nv_bfloat16, false); }
+#undef CB_MOE
+    return cb_last_error();
+}
+
+// The same as cb_moe_tiles for steps of few rows; K a multiple of 8 and 16-byte aligned rows.
+CB_EXPORT int cb_moe_rows_small(int gated, const void* a, int a_stride, const void* w, long expert_stride,
+                                int dtype, int N, int K, const int* plan, int E, int max_tiles,
+                                const int* sorted_pair, int top, const float* weight, void* out,
+                                int out_stride, void* stream) {
+    if (max_tiles <= 0) return 0;
+    if (K % 8 || a_stride % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return CB_ERR_UNSUPPORTED;
+    // enough blocks to keep the memory busy: about four to an SM over all tiles
+    int chunks = (4 * 148 + max_tiles - 1) / max_tiles;
+    int per_block = (N + chunks - 1) / chunks;
+    per_block = per_block < 8 ? 8 : per_block;
+    const dim3 grid(max_tiles, (N + per_block - 1) / per_block), block(256);
+    const size_t smem = (size_t)4 * K * (dtype == CB_F32 ? 4 : 2);      // the staged rows
+    if (smem > 64 * 1024) return CB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+#define CB_MOE(TT, GG)                                                                                  \
+    do {                                                                                                \
+        if (smem > 48 * 1024) {                                                                         \
+            static bool configured = false;                                                             \
+            if (!configured) {                                                                          \
+                cudaError_t err = cudaFuncSetAttribute(moe_rows_small_kernel<TT, GG, 4>,                \
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024); \
+                if (err != cudaSuccess) return (int)err;                                                \
+                configured = true;                                                                      \
+            }                                                                                           \
+        }                                                                                               \
+        cb_launch(moe_rows_small_kernel<TT, GG, 4>, grid, block, smem, s, (const TT*)a, a_stride,       \
+                  (const TT*)w, expert_stride, N, K, plan, E, max_tiles, sorted_pair, top, weight, out, \
+                  out_stride, per_block);                                                               \
+    } while (0)
     if (dtype == CB_F32) { if (gated) CB_MOE(float, true); else CB_MOE(float, false); }
     else { if (gated) CB_MOE(__nv_bfloat16, true); else CB_MOE(__nv_bfloat16, false); }
 #undef CB_MOE

@@ -41,3 +41,27 @@ def head_gate(x, logit, n_heads: int, head_width: int) -> None:
     _check(lib.cb_head_gate(_ptr(x), _c_int(x.stride(0)), _c_int(_code(x.dtype)), _ptr(logit),
                             _c_int(logit.stride(0)), _c_int(x.shape[0]), _c_int(n_heads),
                             _c_int(head_width), _stream()), "head_gate")
+
+
+SMALL_ROWS = 16      # steps of up to this many rows take the heads' products in one launch
+
+
+def heads_linear(a, a_head: int, w, out, out_head: int) -> None:
+    """out[t, h * out_head + n] = sum_k a[t, h * a_head + k] * w[h, n, k] for every head h of
+    `w` [heads, N, K].  Steps of a few bfloat16 rows run as one launch whose warps each read one
+    weight row once; otherwise one product per head through `ops.linear` (the tensor-core tiles
+    for many bfloat16 rows; in float32 always, so that a row's sums never depend on the step)."""
+    from . import linear
+    heads, n, k = w.shape
+    if a.dtype == torch.bfloat16 and a.shape[0] <= SMALL_ROWS:
+        _need_cuda(a, w, out)
+        if a.stride(1) != 1 or out.stride(1) != 1 or not w.is_contiguous() or out.dtype != a.dtype:
+            raise KernelError("heads_linear: contiguous rows of one dtype and contiguous weights")
+        lib = build.load("latent_attention")
+        _check(lib.cb_heads_linear_small(_ptr(a), _c_int(a.stride(0)), _c_int(a_head), _ptr(w), _ptr(out),
+                                         _c_int(out.stride(0)), _c_int(out_head), _c_int(_code(a.dtype)),
+                                         _c_int(a.shape[0]), _c_int(heads), _c_int(n), _c_int(k), _stream()),
+               "heads_linear (few rows)")
+        return
+    for i in range(heads):
+        linear(a[:, i * a_head:i * a_head + k], w[i], out[:, i * out_head:i * out_head + n])

@@ -56,6 +56,25 @@ def expert_tiles(gated: bool, a, w, n_out: int, plan, n_experts: int, tiles: int
            "moe gate/up" if gated else "moe down")
 
 
+def expert_rows_small(gated: bool, a, w, n_out: int, plan, n_experts: int, tiles: int, sorted_pair,
+                      top: int, weight, out) -> bool:
+    """`expert_tiles` for steps of few rows: every weight row is read once by one warp.  False:
+    the sizes do not allow it (K not a multiple of 8, rows not 16-byte aligned)."""
+    _need_cuda(a, w, plan, sorted_pair, weight, out)
+    if a.dtype != w.dtype or a.stride(1) != 1 or not w.is_contiguous() or out.stride(1) != 1:
+        raise KernelError("moe rows: rows and weights of one dtype, contiguous rows")
+    lib = build.load("moe")
+    code = lib.cb_moe_rows_small(_c_int(1 if gated else 0), _ptr(a), _c_int(a.stride(0)), _ptr(w),
+                                 ctypes.c_long(w.stride(0)), _c_int(_code(a.dtype)), _c_int(n_out),
+                                 _c_int(w.shape[2]), _ptr(plan), _c_int(n_experts), _c_int(tiles),
+                                 _ptr(sorted_pair), _c_int(top), _ptr(weight), _ptr(out),
+                                 _c_int(out.stride(0)), _stream())
+    if code == 100001:
+        return False
+    _check(code, "moe gate/up (few rows)" if gated else "moe down (few rows)")
+    return True
+
+
 def combine(pair_out, top: int, residual) -> None:
     """residual[t] += sum over the token's choices, in their order."""
     _need_cuda(pair_out, residual)

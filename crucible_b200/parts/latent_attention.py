@@ -79,13 +79,11 @@ class LatentAttention(Mixer):
         freq, mscale = (self.position.frequencies()[0], self.position.magnitude()) if R else (None, 1.0)
         kernels.prepare(proj[:, hq:], proj[:, :hq], qx, self.gain, freq, mscale, self.eps, H, D, C, R,
                         ctx, cache, binding)
-        for i in range(H):
-            ops.linear(proj[:, i * (D + R):i * (D + R) + D], self.uk_t[i], qx[:, i * row:i * row + C])
+        kernels.heads_linear(proj, D + R, self.uk_t, qx, row)
         ox = ctx.scratch("latent.ox", (t, H * row), self.dtype)
         ops.paged_attention(qx, ox, H, 1, row, self.spec.softmax_scale, None, ctx, cache, binding)
         act = ctx.scratch("latent.act", (t, H * E), self.dtype)
-        for i in range(H):
-            ops.linear(ox[:, i * row:i * row + C], self.uv[i], act[:, i * E:(i + 1) * E])
+        kernels.heads_linear(ox, row, self.uv, act, E)
         if self.w_gate is not None:
             logit = ctx.scratch("latent.gate", (t, H), torch.float32)
             ops.linear(h, self.w_gate, logit)

@@ -45,6 +45,13 @@ class ActivatedFeedForward(FeedForward):
 
 
 class MixtureOfExperts(FeedForward):
+    # Steps that hold a portion of a prompt read each expert's row count on the host (bfloat16
+    # engine, see `forward`): such steps are not captured as graphs.  Decode steps are.
+    graph_safe_prompt_steps = False
+    SMALL_MAX_PAIRS = 256        # up to this many pairs the experts' weight rows are read by a warp each
+    SORTED_MIN_PAIRS = 256       # from this many (token, expert) pairs on, a prompt step's experts
+                                 # run as one product each over their rows side by side
+
     def __init__(self, spec: FeedForwardSpec):
         self.spec = spec
         self.n = int(spec.option("experts", 0))
@@ -92,9 +99,30 @@ class MixtureOfExperts(FeedForward):
         plan = ctx.scratch("moe.plan", (kernels.plan_ints(n, tiles),), torch.int32)
         kernels.route(logits, top, idx, weight, place, self.count, plan, tiles, order)
         act = ctx.scratch("moe.act", (t * top, f), self.dtype)
-        kernels.expert_tiles(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act)
         pair_out = ctx.scratch("moe.pair_out", (t * top, d), torch.float32)
-        kernels.expert_tiles(False, act, self.down, d, plan, n, tiles, order, top, weight, pair_out)
+        if (self.dtype == torch.bfloat16 and t * top >= self.SORTED_MIN_PAIRS
+                and ctx.host.max_new_tokens > 1 and not torch.cuda.is_current_stream_capturing()):
+            # many rows: each expert's rows side by side, one gate/up product with SiLU and one
+            # down product per expert on the tensor cores; the row counts come to the host
+            starts = plan[1:2 + n].tolist()
+            rows = ctx.scratch("moe.rows", (t * top, d), self.dtype)
+            kernels.gather(h, order, top, rows)
+            down = ctx.scratch("moe.down", (t * top, d), torch.float32)
+            for e in range(n):
+                a, b = starts[e], starts[e + 1]
+                if b > a:
+                    ops.linear_swiglu(rows[a:b], self.gate_up[e], act[a:b], ctx)
+                    ops.linear(act[a:b], self.down[e], down[a:b])
+            kernels.scatter(down, order, weight, pair_out)
+        elif (self.dtype == torch.bfloat16 and t * top <= self.SMALL_MAX_PAIRS
+              and kernels.expert_rows_small(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act)):
+            # few rows (decoded tokens): the weights are what moves; a warp per weight row
+            if not kernels.expert_rows_small(False, act, self.down, d, plan, n, tiles, order, top, weight,
+                                             pair_out):
+                kernels.expert_tiles(False, act, self.down, d, plan, n, tiles, order, top, weight, pair_out)
+        else:
+            kernels.expert_tiles(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act)
+            kernels.expert_tiles(False, act, self.down, d, plan, n, tiles, order, top, weight, pair_out)
         kernels.combine(pair_out, top, residual)
         if self.shared is not None:
             self.shared.forward(ctx, h, residual)
