@@ -12,8 +12,9 @@
 //             head's q_rot into the last `rot` columns of q'.
 //   head gate per (token, head): the head's output times sigmoid(logit).
 //
-// Rotation: feature i pairs with i + rot/2; the angle is fp32(position) * freq[i] as an fp32
-// product, cos and sin (fp32) times `mscale`.
+// Rotation: of the `rot` features the first `turned` turn (feature i pairs with i + turned/2),
+// the rest pass unchanged; the angle is fp32(position) * freq[i] as an fp32 product, cos and sin
+// (fp32) times `mscale`.
 #define CB_PDL_BIT 15      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 
@@ -29,13 +30,13 @@ __global__ void latent_prepare_kernel(const T* __restrict__ dkv, int dkv_stride,
                                       const int* __restrict__ row_request,
                                       const int* __restrict__ block_table, int table_stride,
                                       T* __restrict__ pages, int n_heads, int dim, int rank, int rot,
-                                      int page_tokens, int write) {
+                                      int turned, int page_tokens, int write) {
     cb_pdl_trigger();
     cb_pdl_wait();
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const int pos = positions[t];
-    const int half = rot >> 1;
+    const int half = turned >> 1, still = rot - turned;
     const T* src = dkv + (size_t)t * dkv_stride;
     if (write) {
         const int page = block_table[(size_t)row_request[t] * table_stride + pos / page_tokens];
@@ -56,6 +57,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ dkv, int dkv_stride,
             dst[rank + i] = cb_from_float<T>(u * cs - v * sn);
             dst[rank + half + i] = cb_from_float<T>(v * cs + u * sn);
         }
+        for (int i = threadIdx.x; i < still; i += blockDim.x) dst[rank + turned + i] = src[rank + turned + i];
     }
     for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
         const int h = i / half, j = i - h * half;
@@ -67,6 +69,11 @@ __global__ void latent_prepare_kernel(const T* __restrict__ dkv, int dkv_stride,
         const float u = cb_to_float(qr[j]), v = cb_to_float(qr[half + j]);
         dq[j] = cb_from_float<T>(u * cs - v * sn);
         dq[half + j] = cb_from_float<T>(v * cs + u * sn);
+    }
+    for (int i = threadIdx.x; i < n_heads * still; i += blockDim.x) {
+        const int h = i / still, j = turned + (i - h * still);
+        qx[(size_t)t * qx_stride + (size_t)h * (rank + rot) + rank + j] =
+            q[(size_t)t * q_stride + (size_t)h * (dim + rot) + dim + j];
     }
 }
 
@@ -142,22 +149,22 @@ CB_EXPORT int cb_latent_prepare(const void* dkv, int dkv_stride, const void* q, 
                                 int qx_stride, int dtype, const float* gain, const float* freq,
                                 float mscale, float eps, const int* positions, const int* row_request,
                                 const int* block_table, int table_stride, void* pages, int n_rows,
-                                int n_heads, int dim, int rank, int rot, int page_tokens, int write,
-                                void* stream) {
+                                int n_heads, int dim, int rank, int rot, int turned, int page_tokens,
+                                int write, void* stream) {
     if (n_rows <= 0) return 0;
-    if (rot < 0 || (rot & 1) || rank <= 0) return CB_ERR_UNSUPPORTED;
+    if (rot < 0 || turned < 0 || turned > rot || (turned & 1) || rank <= 0) return CB_ERR_UNSUPPORTED;
     const dim3 grid(n_rows), block(rank >= 512 ? 256 : 128);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
         cb_launch(latent_prepare_kernel<float>, grid, block, 0, s, (const float*)dkv, dkv_stride,
                   (const float*)q, q_stride, (float*)qx, qx_stride, gain, freq, mscale, eps, positions,
                   row_request, block_table, table_stride, (float*)pages, n_heads, dim, rank, rot,
-                  page_tokens, write);
+                  turned, page_tokens, write);
     else
         cb_launch(latent_prepare_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)dkv,
                   dkv_stride, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)qx, qx_stride, gain, freq,
                   mscale, eps, positions, row_request, block_table, table_stride, (__nv_bfloat16*)pages,
-                  n_heads, dim, rank, rot, page_tokens, write);
+                  n_heads, dim, rank, rot, turned, page_tokens, write);
     return cb_last_error();
 }
 

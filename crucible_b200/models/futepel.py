@@ -82,8 +82,8 @@ def _mixer(kind: str, raw: Mapping[str, Any], width: int, eps: float, where: str
         if rot_dim:
             rot = KeyReader(_section(raw, "rot", where), where + ".rot")
             dims = rot.integer("dims", rot_dim)
-            if dims != rot_dim or dims % 2:
-                raise ConfigError(f"{where}.rot: 'dims' must be even and equal to 'rot_dim' ({rot_dim}), got {dims}")
+            if dims > rot_dim or dims % 2:
+                raise ConfigError(f"{where}.rot: 'dims' must be even and at most 'rot_dim' ({rot_dim}), got {dims}")
             scaling = None
             if raw["rot"].get("scaling") is not None:
                 sc = KeyReader(_section(raw["rot"], "scaling", where + ".rot"), where + ".rot.scaling")

@@ -8,16 +8,16 @@ from . import KernelError, _c_float, _c_int, _check, _code, _need_cuda, _ptr, _s
 
 
 def prepare(dkv, q, qx, gain, freq, mscale: float, eps: float, n_heads: int, dim: int, rank: int,
-            rot: int, ctx, cache, binding) -> None:
+            rot: int, turned: int, ctx, cache, binding) -> None:
     """Rows of `dkv` are [latent: rank | shared key part: rot], rows of `q` [heads, dim + rot].
     Writes [rmsnorm(latent) * gain | rotated key part] to the token's place in the pages and the
-    rotated last `rot` features of every head of q into the last `rot` of that head in `qx`
-    [heads, rank + rot]."""
+    last `rot` features of every head of q, rotated, into the last `rot` of that head in `qx`
+    [heads, rank + rot].  Of the `rot` features the first `turned` turn, the rest pass unchanged."""
     _need_cuda(dkv, q, qx, gain, freq)
     if dkv.stride(1) != 1 or q.stride(1) != 1 or qx.stride(1) != 1 or not (dkv.dtype == q.dtype == qx.dtype):
         raise KernelError("latent prepare: contiguous rows of one dtype")
-    if rot and (freq is None or freq.dtype != torch.float32 or freq.numel() * 2 != rot):
-        raise KernelError("latent prepare: freq is float32 [rot / 2]")
+    if turned and (freq is None or freq.dtype != torch.float32 or freq.numel() * 2 != turned):
+        raise KernelError("latent prepare: freq is float32 [turned / 2]")
     pages = cache.keys(binding.slot)
     if pages.dtype != dkv.dtype or pages.shape[-1] != rank + rot or cache.kv_heads != 1:
         raise KernelError("latent prepare: the pages hold one row of rank + rot features per token "
@@ -28,7 +28,7 @@ def prepare(dkv, q, qx, gain, freq, mscale: float, eps: float, n_heads: int, dim
         _ptr(dkv), _c_int(dkv.stride(0)), _ptr(q), _c_int(q.stride(0)), _ptr(qx), _c_int(qx.stride(0)),
         _c_int(_code(dkv.dtype)), _ptr(gain), _ptr(freq), _c_float(mscale), _c_float(eps),
         _ptr(ctx.positions), _ptr(ctx.row_request), _ptr(table), _c_int(table.shape[1]), _ptr(pages),
-        _c_int(dkv.shape[0]), _c_int(n_heads), _c_int(dim), _c_int(rank), _c_int(rot),
+        _c_int(dkv.shape[0]), _c_int(n_heads), _c_int(dim), _c_int(rank), _c_int(rot), _c_int(turned),
         _c_int(cache.page_tokens), _c_int(1 if binding.write else 0), _stream()), "latent_prepare")
 
 

@@ -38,10 +38,12 @@ class LatentAttention(Mixer):
         if s.window is not None:
             raise ValueError("latent attention sees every earlier token: it takes no window")
         self.position = (POSITIONS.build(s.position.kind, s.position) if s.position is not None else None)
-        if self.R and (self.position is None or not hasattr(self.position, "frequencies")
-                       or self.position.spec.rotary_dim != self.R):
+        if self.position is not None and (not hasattr(self.position, "frequencies")
+                                          or self.position.spec.rotary_dim > self.R):
             raise ValueError("latent attention: the rotated part needs a position encoding that gives "
-                             "`frequencies()` over exactly rot_dim features")
+                             "`frequencies()` over at most rot_dim features")
+        # of the rot_dim features the encoding's first rotary_dim turn, the rest pass unchanged
+        self.turned = self.position.spec.rotary_dim if self.position is not None else 0
 
     def tensors(self):
         d, H, D, R, E, C = self.spec.width, self.H, self.D, self.R, self.E, self.C
@@ -76,9 +78,10 @@ class LatentAttention(Mixer):
         ops.linear(h, self.w_in, proj)
         cache = ctx.cache(binding.group)
         qx = ctx.scratch("latent.qx", (t, H * row), self.dtype)
-        freq, mscale = (self.position.frequencies()[0], self.position.magnitude()) if R else (None, 1.0)
+        freq, mscale = ((self.position.frequencies()[0], self.position.magnitude()) if self.turned
+                        else (None, 1.0))
         kernels.prepare(proj[:, hq:], proj[:, :hq], qx, self.gain, freq, mscale, self.eps, H, D, C, R,
-                        ctx, cache, binding)
+                        self.turned, ctx, cache, binding)
         kernels.heads_linear(proj, D + R, self.uk_t, qx, row)
         ox = ctx.scratch("latent.ox", (t, H * row), self.dtype)
         ops.paged_attention(qx, ox, H, 1, row, self.spec.softmax_scale, None, ctx, cache, binding)

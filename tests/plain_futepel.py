@@ -106,12 +106,13 @@ def yarn_frequencies(dims, base, scaling, dtype):
 
 
 def rotate_half(x, positions, freq, mscale):
-    """x: [T, heads, dims]: feature i pairs with i + dims/2."""
-    half = x.shape[-1] // 2
+    """x: [T, heads, n]: the first dims = 2 len(freq) features turn, feature i with i + dims/2;
+    the rest pass unchanged."""
+    half = freq.shape[0]
     ang = positions.to(x.dtype)[:, None] * freq[None, :]
     c, s = (torch.cos(ang) * mscale)[:, None, :], (torch.sin(ang) * mscale)[:, None, :]
-    a, b = x[..., :half], x[..., half:]
-    return torch.cat([a * c - b * s, b * c + a * s], -1)
+    a, b = x[..., :half], x[..., half:2 * half]
+    return torch.cat([a * c - b * s, b * c + a * s, x[..., 2 * half:]], -1)
 
 
 def latent_attention(h, w, cfg, eps, positions):

@@ -38,7 +38,7 @@ def test_the_architecture_is_registered_and_parsed():
 @pytest.mark.parametrize("edit,word", [
     (lambda c: c["layers"][0].update(type="conv"), "unknown layer type"),
     (lambda c: c["layers"][0]["mixer"].pop("kv_rank"), "kv_rank"),
-    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=6), "rot_dim"),
+    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=10), "rot_dim"),
     (lambda c: c["layers"][0]["mlp"]["router"].update(top=7), "top"),
     (lambda c: c["layers"][1]["mlp"].update(kind="glu"), "kind"),
     (lambda c: c["embedding"]["bigram"].pop("mul_cur"), "mul_cur"),

@@ -263,9 +263,9 @@ def test_mamba2(dtype, heads, vdim, state, groups, conv, parts, width):
 # latent attention: keys far back, at page borders, at the row's own position
 # ---------------------------------------------------------------------------
 
-def _latent_spec(heads, dim, rot, vdim, rank, width, scaling):
+def _latent_spec(heads, dim, rot, vdim, rank, width, scaling, turned=None):
     from crucible_b200.config.model_config import MixerSpec, PositionSpec
-    position = PositionSpec(kind="rope_yarn", rotary_dim=rot, theta=1000.0, max_positions=0,
+    position = PositionSpec(kind="rope_yarn", rotary_dim=turned or rot, theta=1000.0, max_positions=0,
                             scaling=tuple(scaling.items()) if scaling else None)
     return MixerSpec(kind="latent_attention", width=width, n_heads=heads, n_kv_heads=1, head_dim=dim,
                      softmax_scale=0.25, position=position,
@@ -277,6 +277,7 @@ def _latent_spec(heads, dim, rot, vdim, rank, width, scaling):
 @pytest.mark.parametrize("heads,dim,rot,vdim,rank,width,page,scaling",
                          [(2, 24, 8, 16, 40, 48, 8, {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}),
                           (4, 32, 32, 32, 96, 64, 16, None),            # rows of 128: tensor cores in bfloat16
+                          (2, 16, 16, 16, 48, 32, 8, None),             # rows of 64
                           (3, 10, 6, 14, 21, 40, 4, {"factor": 2.0, "original": 32, "fast": 4.0, "slow": 1.0})])
 def test_latent_attention_finds_marked_keys(dtype, heads, dim, rot, vdim, rank, width, page, scaling):
     """Feature 0 of the input is 1 for every token and feature 1 is large for a few marked
@@ -308,6 +309,16 @@ def test_latent_attention_finds_marked_keys(dtype, heads, dim, rot, vdim, rank, 
     def ref(h, w):
         return plain.latent_attention(h, w, cfg, 1e-5, torch.arange(h.shape[0]))
     _check_mixer(spec, ref, dtype, {0: 270, 1: 3 * page + 1, 3: 2}, page=page, edit=edit, h_edit=h_edit, std=0.1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_latent_attention_turns_a_part_of_the_rotated_features(dtype):
+    heads, dim, rot, vdim, rank, width, turned = 2, 12, 12, 8, 20, 32, 8
+    spec = _latent_spec(heads, dim, rot, vdim, rank, width, None, turned=turned)
+    cfg = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "scale": 0.25,
+           "rot": {"base": 1000.0, "dims": turned, "scaling": None}}
+    _check_mixer(spec, lambda h, w: plain.latent_attention(h, w, cfg, 1e-5, torch.arange(h.shape[0])), dtype,
+                 {0: 40, 1: 9}, page=8)
 
 
 def test_latent_attention_marked_keys_matter():
