@@ -108,6 +108,13 @@ def cmd_inspect(args) -> int:
               f"head size {branch.head_dim}, window {branch.window}, scale {scale}, "
               f"options {dict(branch.extra)}")
     print(f"layer 0 ffn    {cfg.layers[0].feed_forward.kind}: {cfg.layers[0].feed_forward.intermediate}")
+    if len(set(kinds)) > 1:
+        for i, l in enumerate(cfg.layers[1:], 1):
+            print(f"layer {i} mixer  {l.mixer.kind}: {l.mixer.n_heads} heads, head size {l.mixer.head_dim}, "
+                  f"options {dict(l.mixer.extra)}; ffn {l.feed_forward.kind}: {l.feed_forward.intermediate} "
+                  f"{dict(l.feed_forward.extra)}")
+    if cfg.embedding.kind != "token":
+        print(f"embedding      {cfg.embedding.kind} {dict(cfg.embedding.extra)}")
     print(f"norm           {cfg.final_norm.kind} eps {cfg.final_norm.eps}")
     print(f"cache groups   {len(model.cache_groups)}; state bytes per request {model.state_bytes}")
     f = SafetensorsFile(os.path.join(args.model, "model.safetensors"))

@@ -40,7 +40,10 @@ class PreNormBlock(Arrangement):
         if announce is None:
             return
         norm, consumer = ahead if ahead is not None else (None, None)
+        # (a consumer with `takes_prenormed = False` fuses the norm of a few rows into its first
+        # product but has no product that takes rows a product before it left ahead of their norm)
         if (norm is not None and getattr(consumer, "fuses_norm", False)
+                and getattr(consumer, "takes_prenormed", True)
                 and getattr(norm, "supports_ahead", False)):
             announce(norm, x)
         else:

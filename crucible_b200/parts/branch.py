@@ -62,13 +62,14 @@ def run_products(ctx, owner, branches: List[BranchMixer], scales, bindings, h, o
                  w_in, w_gates, w_out) -> None:
     t = h.shape[0]
     tag = type(owner).__name__
-    proj = ctx.scratch(f"{tag}.proj", (t, w_in.shape[0]), h.dtype)
+    dtype = w_in.dtype          # the engine dtype (h may be rows that are not yet normalised)
+    proj = ctx.scratch(f"{tag}.proj", (t, w_in.shape[0]), dtype)
     ops.linear(h, w_in, proj)
     gates = None
     if w_gates is not None:
         gates = ctx.scratch(f"{tag}.gates", (t, w_gates.shape[0]), torch.float32)
         ops.linear(h, w_gates, gates)
-    act = ctx.scratch(f"{tag}.act", (t, w_out.shape[1]), h.dtype)
+    act = ctx.scratch(f"{tag}.act", (t, w_out.shape[1]), dtype)
     p = g = a = 0
     for branch, scale, binding in zip(branches, scales, bindings):
         np_, na = branch.input_weight().shape[0], branch.output_weight().shape[1]

@@ -25,6 +25,9 @@ from .base import MIXERS, POSITIONS, CacheNeed, Mixer, TensorDecl
 
 
 class LatentAttention(Mixer):
+    fuses_norm = True          # h goes into products only: few rows are normalised on their way in
+    takes_prenormed = False
+
     def __init__(self, spec: MixerSpec):
         s = self.spec = spec
         self.H, self.D = s.n_heads, s.head_dim

@@ -21,6 +21,9 @@ from .swiglu import SwiGLU
 
 
 class ActivatedFeedForward(FeedForward):
+    fuses_norm = True          # h goes into one product: few rows are normalised on their way in
+    takes_prenormed = False
+
     def __init__(self, spec: FeedForwardSpec):
         self.spec = spec
         self.kind = str(spec.option("activation", "relu2"))

@@ -219,6 +219,9 @@ class WKVMixer(Mixer):
 
 
 class StateSpaceMixer(BranchMixer):
+    fuses_norm = True          # h goes into products only: few rows are normalised on their way in
+    takes_prenormed = False
+
     def __init__(self, spec: MixerSpec):
         s = self.spec = spec
         self.H, self.G, self.N = s.n_heads, s.n_kv_heads, s.head_dim

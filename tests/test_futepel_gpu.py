@@ -175,3 +175,23 @@ def test_the_learned_positions_bound_a_request(tmp_path):
     with pytest.raises(StepError):
         engine.step([StepEntry("a", helpers.random_tokens(211, 41, 1), [])])
     assert not engine.has_request("a")
+
+
+def test_command_line(tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    folder = cases.make_folder(tmp_path, "fu-a")
+    tool = os.path.join(os.path.dirname(os.path.abspath(__file__)), os.pardir, "bin", "llm-engine")
+    proc = subprocess.run([sys.executable, tool, "generate", folder, "--prompt-ids", "5,17,3,200,5,17",
+                           "--max-tokens", "6", "--temperature", "0", "--dtype", "float32", "--graph"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    config, tensors = plain.read_folder(folder)
+    assert json.loads(proc.stdout.strip().splitlines()[0])["tokens"] == plain.greedy(config, tensors, [5, 17, 3, 200, 5, 17], 6)
+    proc = subprocess.run([sys.executable, tool, "inspect", folder], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    for word in ("Futepel", "latent_attention+moe", "wkv+dense_act", "mamba2+none", "token_hashed_positions",
+                 "cache groups   2"):
+        assert word in proc.stdout, (word, proc.stdout)
