@@ -89,7 +89,7 @@ def futepel(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab
               "mixer": {"heads": heads, "dim": head_dim, "rot_dim": 64, "vdim": head_dim, "kv_rank": 192,
                         "scale": (head_dim + 64) ** -0.5,
                         "rot": {"base": 10000.0, "dims": 64,
-                                "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+                                "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}}
     cycle = [mamba, dict(wkv, mlp=moe), dict(wkv, mlp=dense), latent]
     return {"architecture": "Futepel", "vocab": vocab, "width": width, "max_positions": max_positions,
             "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 1000003,
