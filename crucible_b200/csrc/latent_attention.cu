@@ -98,7 +98,9 @@ __global__ void head_gate_kernel(T* __restrict__ x, int x_stride, const float* _
 template <typename T, int ROWS>
 __global__ void heads_linear_small_kernel(const T* __restrict__ a, int a_stride, int a_head,
                                           const T* __restrict__ w, T* __restrict__ out, int out_stride,
-                                          int out_head, int n_rows, int n_heads, int N, int K) {
+                                          int out_head, int n_rows, int n_heads, int N, int K,
+                                          const float* __restrict__ gate_logit, int gate_stride) {
+    // gate_logit (optional): fp32 [rows][heads]; the head's results times sigmoid(logit)
     cb_pdl_trigger();
     cb_pdl_wait();
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -119,9 +121,12 @@ __global__ void heads_linear_small_kernel(const T* __restrict__ a, int a_stride,
         }
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-            const float v = cb_warp_sum(acc[r]);
-            if (lane == 0 && t0 + r < n_rows)
+            float v = cb_warp_sum(acc[r]);
+            if (lane == 0 && t0 + r < n_rows) {
+                if (gate_logit != nullptr)
+                    v *= 1.0f / (1.0f + expf(-gate_logit[(size_t)(t0 + r) * gate_stride + h]));
                 out[(size_t)(t0 + r) * out_stride + (size_t)h * out_head + n] = cb_from_float<T>(v);
+            }
         }
     }
 }
@@ -130,18 +135,19 @@ __global__ void heads_linear_small_kernel(const T* __restrict__ a, int a_stride,
 
 CB_EXPORT int cb_heads_linear_small(const void* a, int a_stride, int a_head, const void* w, void* out,
                                     int out_stride, int out_head, int dtype, int n_rows, int n_heads,
-                                    int N, int K, void* stream) {
+                                    int N, int K, const float* gate_logit, int gate_stride, void* stream) {
     if (n_rows <= 0 || n_heads <= 0 || N <= 0) return 0;
     const int warps = 4;
     const dim3 grid((unsigned)(((long)n_heads * N + warps - 1) / warps)), block(warps * 32);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
         cb_launch(heads_linear_small_kernel<float, 8>, grid, block, 0, s, (const float*)a, a_stride, a_head,
-                  (const float*)w, (float*)out, out_stride, out_head, n_rows, n_heads, N, K);
+                  (const float*)w, (float*)out, out_stride, out_head, n_rows, n_heads, N, K, gate_logit,
+                  gate_stride);
     else
         cb_launch(heads_linear_small_kernel<__nv_bfloat16, 8>, grid, block, 0, s, (const __nv_bfloat16*)a,
                   a_stride, a_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, out_head, n_rows,
-                  n_heads, N, K);
+                  n_heads, N, K, gate_logit, gate_stride);
     return cb_last_error();
 }
 

@@ -46,11 +46,13 @@ def head_gate(x, logit, n_heads: int, head_width: int) -> None:
 SMALL_ROWS = 16      # steps of up to this many rows take the heads' products in one launch
 
 
-def heads_linear(a, a_head: int, w, out, out_head: int) -> None:
+def heads_linear(a, a_head: int, w, out, out_head: int, gate_logit=None) -> None:
     """out[t, h * out_head + n] = sum_k a[t, h * a_head + k] * w[h, n, k] for every head h of
     `w` [heads, N, K].  Steps of a few bfloat16 rows run as one launch whose warps each read one
     weight row once; otherwise one product per head through `ops.linear` (the tensor-core tiles
-    for many bfloat16 rows; in float32 always, so that a row's sums never depend on the step)."""
+    for many bfloat16 rows; in float32 always, so that a row's sums never depend on the step).
+    `gate_logit` (float32 [rows, heads]): every head's results times sigmoid(logit), in the same
+    launch for few rows, by `head_gate` otherwise."""
     from . import linear
     heads, n, k = w.shape
     if a.dtype == torch.bfloat16 and a.shape[0] <= SMALL_ROWS:
@@ -60,8 +62,15 @@ def heads_linear(a, a_head: int, w, out, out_head: int) -> None:
         lib = build.load("latent_attention")
         _check(lib.cb_heads_linear_small(_ptr(a), _c_int(a.stride(0)), _c_int(a_head), _ptr(w), _ptr(out),
                                          _c_int(out.stride(0)), _c_int(out_head), _c_int(_code(a.dtype)),
-                                         _c_int(a.shape[0]), _c_int(heads), _c_int(n), _c_int(k), _stream()),
+                                         _c_int(a.shape[0]), _c_int(heads), _c_int(n), _c_int(k),
+                                         _ptr(gate_logit),
+                                         _c_int(gate_logit.stride(0) if gate_logit is not None else 0),
+                                         _stream()),
                "heads_linear (few rows)")
         return
     for i in range(heads):
         linear(a[:, i * a_head:i * a_head + k], w[i], out[:, i * out_head:i * out_head + n])
+    if gate_logit is not None:
+        if out.shape[1] != heads * out_head:
+            raise KernelError("heads_linear: a gate needs the heads' results side by side")
+        head_gate(out, gate_logit, heads, out_head)

@@ -89,11 +89,11 @@ class LatentAttention(Mixer):
         ox = ctx.scratch("latent.ox", (t, H * row), self.dtype)
         ops.paged_attention(qx, ox, H, 1, row, self.spec.softmax_scale, None, ctx, cache, binding)
         act = ctx.scratch("latent.act", (t, H * E), self.dtype)
-        kernels.heads_linear(ox, row, self.uv, act, E)
+        logit = None
         if self.w_gate is not None:
             logit = ctx.scratch("latent.gate", (t, H), torch.float32)
             ops.linear(h, self.w_gate, logit)
-            kernels.head_gate(act, logit, H, E)
+        kernels.heads_linear(ox, row, self.uv, act, E, gate_logit=logit)
         ops.linear(act, self.w_out, residual, accumulate=True, closes=ctx)
 
 
